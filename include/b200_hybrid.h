@@ -107,9 +107,16 @@ B200H_API int b200h_gated_rms(const void* o, const void* w, const void* gate, in
 
 /* softmax(router x) over all experts; ids / wts [n, top]: the top largest and their scores. */
 B200H_API int b200h_route(const void* x, const void* router, int n, int width, int experts, int top, void* ids, void* wts, void* stream);
+/* The same with x as float or T (x_dtype) and a choice of scores: score_fn 0 = softmax over all experts, 1 = sigmoid of every
+ * logit on its own (the weights are the chosen experts' sigmoids, not renormalised). */
+B200H_API int b200h_route_scored(const void* x, int x_dtype, const void* router, int n, int width, int experts, int top, int score_fn,
+                                 void* ids, void* wts, void* stream);
 
-/* Routed experts for a step of few rows (an expert's weights are read once for all rows that chose it):
- * out[t, k] = wts[t, k] * down_e (silu(gate_e x[t]) * (up_e x[t])), e = ids[t, k]. */
+/* Routed experts for a step of few rows (an expert's weights are read once for all rows that chose it), e = ids[t, k], w = wts[t, k]:
+ *   act 0, scale_input 0:  out[t, k] = w * down_e (silu(gate_e x[t]) * (up_e x[t]))
+ *   act 1 (no gate matrix): out[t, k] = w * down_e relu(up_e x[t])^2
+ *   scale_input 1: the score multiplies the expert's input instead, expert_e(w x[t]); it is applied to the first products
+ *   (linear in x), so the scaled input is never rounded to T. */
 typedef struct b200h_expert_args {
     int n, width, ff, experts, top, dtype;
     const void* x;           /* T [n, width] */
@@ -123,6 +130,8 @@ typedef struct b200h_expert_args {
     void* counts;            /* int [experts] scratch */
     void* lists;             /* int [experts, n * top] scratch */
     void* stream;
+    int act;                 /* 0: silu(gate) * up; 1: relu(up)^2 (gate is not read) */
+    int scale_input;         /* 0: the score scales the expert's output; 1: its input */
 } b200h_expert_args;
 B200H_API int b200h_experts(const b200h_expert_args* args);
 
@@ -130,7 +139,7 @@ B200H_API int b200h_experts(const b200h_expert_args* args);
 B200H_API int b200h_silu_mul(const void* g, const void* u, void* out, int64_t count, int dtype, void* stream);
 
 /* out[slot[r]] = wts[slot[r]] * src[r]: rows grouped by expert (src T [rows, width]) back to their (row, choice) places
- * (out float [rows, width], wts float [rows], slot int [rows]). */
+ * (out float [rows, width], wts float [rows] or NULL for 1, slot int [rows]). */
 B200H_API int b200h_weighted_scatter(const void* src, const void* slot, const void* wts, void* out, int rows, int width, int dtype,
                                      void* stream);
 
@@ -154,7 +163,8 @@ B200H_API int b200h_relu2(void* x, int64_t count, int dtype, void* stream);
  * Query head h reads key/value head h / (heads / kv_heads).  For the query at position i and a key at position j,
  * max(0, i - window + 1) <= j <= i (window 0: every j <= i):
  *   s = scale * (q . k);  s <- softcap * tanh(s / softcap) if softcap > 0;  s <- s - r1[h] * ln(1 + r2[h] * (i - j)) if r1;
- *   weight = softmax over j;  weight_h <- sum_g talk[h, g] * weight_g if talk;  out_h = sum_j weight_h(j) * v_j;
+ *   weight = softmax over j (with exp(sink[h]) added to the denominator if sink: a score that carries no value);
+ *   weight_h <- sum_g talk[h, g] * weight_g if talk;  out_h = sum_j weight_h(j) * v_j;
  *   y = out * sigmoid(gate) if gate.
  * Cache entry of a position inside its page (page address + layer_off): the normed key as T at [pos % block_len][kv_heads * dim],
  * and, v_off bytes further, the value as T at [pos % block_len][kv_heads * vdim]. */
@@ -186,10 +196,71 @@ typedef struct b200h_window_args {
     int64_t layer_off, v_off;
     int dtype;
     void* stream;
+    const void* sink;        /* float [heads] or NULL */
 } b200h_window_args;
 /* Bias, norm of query and key, cache store of key and value (fills qn). */
 B200H_API int b200h_window_prep(const b200h_window_args* args);
 /* Attention of the step's rows over the cache (fills y); the step's own rows must have been stored by b200h_window_prep. */
 B200H_API int b200h_window_attention(const b200h_window_args* args);
+
+/* ---- parallel blocks (both sublayers read the same stream), convolved rotary attention, state-space mixer ---- */
+
+/* x[t] += mult * (mix[t] + sum_p ff[t, p]) + add[t] + extra, then h1[t] = x[t] / rms(x[t]) * w1 and h2[t] = ... * w2 as T.
+ * mix T [n, width], ff float [n, parts, width], add float [n, width], extra T [width], h1, h2: each optional (NULL);
+ * w1 / w2 float [width] hold the full factor. */
+B200H_API int b200h_parallel_residual_norm(void* x, const void* mix, const void* ff, int parts, float mult, const void* add, const void* extra,
+                                           const void* w1, const void* w2, int n, int width, float eps, void* h1, void* h2, int dtype,
+                                           void* stream);
+
+/* out[t, c] = act(bias[c] + sum_j w[c, j] * u[t - taps + 1 + j, c]) as float [n, channels]; u T with row stride ld; w float
+ * [channels, taps]; bias float [channels] or NULL; act 0 none, 1 silu.  Rows before an entry's first come from its state (float
+ * [taps - 1, channels] at state + seq_slot[s] * slot_stride), which is then advanced by the step. */
+B200H_API int b200h_short_conv(const void* u, int64_t ld, const void* w, const void* bias, int act, void* state, int64_t slot_stride,
+                               const void* tok_seq, const void* cu_q, const void* seq_slot, void* out, int n, int batch, int channels,
+                               int taps, int dtype, void* stream);
+
+/* Per head h (group h / (heads / groups)): dt = softplus(dt + dt_bias[h]); S <- exp(-exp(a_log[h]) dt) S + dt B x^T;
+ * out = S^T C + skip[h] x (float [n, heads * vdim]).  xbc float [n, heads * vdim + 2 * groups * nstate] = x | B | C;
+ * dt T with row stride ld_dt, one column per head; state float [heads, vdim, nstate] at state + seq_slot[s] * slot_stride. */
+B200H_API int b200h_ssm_scan(const void* xbc, const void* dt, int64_t ld_dt, const void* dt_bias, const void* a_log, const void* skip,
+                             void* state, int64_t slot_stride, const void* cu_q, const void* seq_slot, int batch, int heads, int vdim,
+                             int nstate, int groups, void* out, int dtype, void* stream);
+
+/* out[t] = unit_rms_per_group(y[t] * silu(gate[t])) * w as T; y float [n, count], gate T with row stride ld_gate, `groups` equal parts. */
+B200H_API int b200h_gate_group_norm(const void* y, const void* gate, int64_t ld_gate, const void* w, int n, int count, int groups, float eps,
+                                    void* out, int dtype, void* stream);
+
+/* Preparation of an attention layer whose stacked projection qk (T [n, ld]: heads * dim query columns, then kv_heads * dim key
+ * columns) passes a short causal convolution per channel (conv float [channels, taps], state float [taps - 1, channels] per slot),
+ * then a rotation of every head's first 2 * rot.pairs dimensions, then a division by the head's root mean square.  The cache gets
+ * the normed key (T, at layer_off) and, as the VALUE, the convolved key before rotation and norm (T, at layer_off + v_off),
+ * laid out as b200h_window_args describes; qn gets the queries (float [n, heads * dim]). */
+typedef struct b200h_conv_prep_args {
+    int n, batch, heads, kv_heads, dim, taps, block_len;
+    float eps;
+    b200h_rotary rot;
+    const void* qk;
+    int64_t ld;
+    const void* conv;
+    void* state;
+    int64_t slot_stride;
+    void* qn;
+    const void* tok_seq;     /* int [n] */
+    const void* tok_pos;     /* int [n] */
+    const void* cu_q;        /* int [batch + 1] */
+    const void* seq_slot;    /* int [batch] */
+    const void* block_ptrs;
+    const void* cu_blocks;
+    int64_t layer_off, v_off;
+    int dtype;
+    void* stream;
+} b200h_conv_prep_args;
+B200H_API int b200h_conv_rope_prep(const b200h_conv_prep_args* args);
+
+/* x <- cap * tanh(x / cap) in place (float). */
+B200H_API int b200h_softcap(void* x, int64_t count, float cap, void* stream);
+
+/* u[r, :] <- relu(scale[r] * u[r, :])^2 in place (u T [rows, cols], scale float [rows] or NULL). */
+B200H_API int b200h_scaled_relu2(void* u, const void* scale, int rows, int cols, int dtype, void* stream);
 
 #endif

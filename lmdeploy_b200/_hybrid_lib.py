@@ -34,6 +34,7 @@ class ExpertArgs(C.Structure):
         ("n", C.c_int), ("width", C.c_int), ("ff", C.c_int), ("experts", C.c_int), ("top", C.c_int), ("dtype", C.c_int),
         ("x", C.c_void_p), ("gate", C.c_void_p), ("up", C.c_void_p), ("down", C.c_void_p), ("ids", C.c_void_p), ("wts", C.c_void_p),
         ("out", C.c_void_p), ("mid", C.c_void_p), ("counts", C.c_void_p), ("lists", C.c_void_p), ("stream", C.c_void_p),
+        ("act", C.c_int), ("scale_input", C.c_int),
     ]
 
 
@@ -47,9 +48,24 @@ class WindowArgs(C.Structure):
         ("r1", C.c_void_p), ("r2", C.c_void_p), ("talk", C.c_void_p), ("gate", C.c_void_p), ("ld_gate", C.c_int64),
         ("ml", C.c_void_p), ("o_part", C.c_void_p), ("scores", C.c_void_p), ("score_ld", C.c_int64), ("y", C.c_void_p),
         ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("block_ptrs", C.c_void_p), ("cu_blocks", C.c_void_p),
-        ("layer_off", C.c_int64), ("v_off", C.c_int64), ("dtype", C.c_int), ("stream", C.c_void_p),
+        ("layer_off", C.c_int64), ("v_off", C.c_int64), ("dtype", C.c_int), ("stream", C.c_void_p), ("sink", C.c_void_p),
     ]
 
+
+class ConvPrepArgs(C.Structure):
+    """b200h_conv_prep_args."""
+    _fields_ = [
+        ("n", C.c_int), ("batch", C.c_int), ("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("taps", C.c_int),
+        ("block_len", C.c_int), ("eps", C.c_float), ("rot", Rotary),
+        ("qk", C.c_void_p), ("ld", C.c_int64), ("conv", C.c_void_p), ("state", C.c_void_p), ("slot_stride", C.c_int64),
+        ("qn", C.c_void_p), ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("cu_q", C.c_void_p), ("seq_slot", C.c_void_p),
+        ("block_ptrs", C.c_void_p), ("cu_blocks", C.c_void_p), ("layer_off", C.c_int64), ("v_off", C.c_int64), ("dtype", C.c_int),
+        ("stream", C.c_void_p),
+    ]
+
+
+SCORE_FN = {"softmax": 0, "sigmoid": 1}
+EXPERT_ACT = {"silu_gate": 0, "relu2": 1}
 
 _lib = None
 P, I, L64, F = C.c_void_p, C.c_int, C.c_int64, C.c_float
@@ -87,6 +103,14 @@ def load():
     lib.b200h_relu2.argtypes = [P, L64, I, P]
     lib.b200h_window_prep.argtypes = [C.POINTER(WindowArgs)]
     lib.b200h_window_attention.argtypes = [C.POINTER(WindowArgs)]
+    lib.b200h_route_scored.argtypes = [P, I, P, I, I, I, I, I, P, P, P]
+    lib.b200h_parallel_residual_norm.argtypes = [P, P, P, I, F, P, P, P, P, I, I, F, P, P, I, P]
+    lib.b200h_short_conv.argtypes = [P, L64, P, P, I, P, L64, P, P, P, P, I, I, I, I, I, P]
+    lib.b200h_ssm_scan.argtypes = [P, P, L64, P, P, P, P, L64, P, P, I, I, I, I, I, P, I, P]
+    lib.b200h_gate_group_norm.argtypes = [P, P, L64, P, I, I, I, F, P, I, P]
+    lib.b200h_conv_rope_prep.argtypes = [C.POINTER(ConvPrepArgs)]
+    lib.b200h_softcap.argtypes = [P, L64, F, P]
+    lib.b200h_scaled_relu2.argtypes = [P, P, I, I, I, P]
     _lib = lib
     return lib
 

@@ -458,15 +458,17 @@ __global__ void gated_rms_kernel(const float* __restrict__ o, const float* __res
 }
 
 // ------------------------------------------------------------------------------------------------ routed experts
-// Router: logits = router x (float), softmax over all experts, the `top` largest (ties: the lower index), their scores as weights.
-__global__ void route_kernel(const float* __restrict__ x, const float* __restrict__ router, int width, int experts, int top,
+// Router: logits = router x (float); scores = softmax over all experts (score_fn 0) or the sigmoid of every logit on its own
+// (score_fn 1); the `top` largest (ties: the lower index), their scores as weights.  x is float or T.
+template <typename TI>
+__global__ void route_kernel(const TI* __restrict__ x, const float* __restrict__ router, int width, int experts, int top, int score_fn,
                              int* __restrict__ ids, float* __restrict__ wts)
 {
     extern __shared__ float sm[];
     float* xs = sm;
     float* z = sm + width;
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = x[(size_t)t * width + i];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(x[(size_t)t * width + i]);
     __syncthreads();
     for (int e = warp; e < experts; e += nw) {
         const float* row = router + (size_t)e * width;
@@ -477,11 +479,16 @@ __global__ void route_kernel(const float* __restrict__ x, const float* __restric
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        float mx = z[0];
-        for (int e = 1; e < experts; ++e) mx = fmaxf(mx, z[e]);
-        float sum = 0.f;
-        for (int e = 0; e < experts; ++e) { z[e] = expf(z[e] - mx); sum += z[e]; }
-        const float inv = 1.0f / sum;
+        float inv = 1.0f;
+        if (score_fn == 1) {
+            for (int e = 0; e < experts; ++e) z[e] = sigmoid_f(z[e]);
+        } else {
+            float mx = z[0];
+            for (int e = 1; e < experts; ++e) mx = fmaxf(mx, z[e]);
+            float sum = 0.f;
+            for (int e = 0; e < experts; ++e) { z[e] = expf(z[e] - mx); sum += z[e]; }
+            inv = 1.0f / sum;
+        }
         for (int k = 0; k < top; ++k) {
             int best = -1;
             float bv = -1.0f;
@@ -499,8 +506,11 @@ __global__ void route_kernel(const float* __restrict__ x, const float* __restric
 // expert_rows_kernel gives a block 32 weight rows of one expert and walks that expert's entries eight at a time: the
 // eight input rows sit in shared memory as T, a warp takes one weight row at a time, every lane reads its 16-byte pieces of
 // the row once and feeds eight float accumulators, and the warp reduces them.
-//   DUAL: out[i, r] = silu(gate_e[r] . x) * (up_e[r] . x) as T        (x = the row's stream as T, K = width, R = ff)
-//   else: out[i, r] = wts[i] * (down_e[r] . mid[i]) as float           (K = ff, R = width)
+//   MODE 1: out[i, r] = silu(w gate_e[r] . x) * (w up_e[r] . x) as T     (x = the row's stream as T, K = width, R = ff)
+//   MODE 2: out[i, r] = relu(w up_e[r] . x)^2 as T                       (an expert without a gate matrix)
+//   MODE 0: out[i, r] = w * (down_e[r] . mid[i]) as float                (K = ff, R = width)
+// w = wts[i], or 1 when wts is nullptr: a design whose router score scales the expert's INPUT gives the score to the first
+// product (the first map is linear, so scaling its result is scaling its input, without rounding the scaled input to T).
 // The order of an expert's list depends on the atomics' order; every entry's result lands in its own place, so the numbers do not.
 __global__ void expert_lists_kernel(const int* __restrict__ ids, int entries, int experts, int* __restrict__ counts, int* __restrict__ lists)
 {
@@ -542,12 +552,13 @@ __device__ __forceinline__ void load_pack<float>(const float* p, float (&v)[4])
     v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
 }
 
-template <typename T, bool DUAL, bool VEC>
+template <typename T, int MODE, bool VEC>
 __global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict__ x, int x_div, const T* __restrict__ wa, const T* __restrict__ wb,
                                    const int* __restrict__ counts, const int* __restrict__ lists, int entries,
                                    const float* __restrict__ wts, int K, int R, void* __restrict__ out_)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr bool DUAL = MODE == 1;
     T* xs = reinterpret_cast<T*>(smem_raw);                     // [kExpertTile][K]
     const int e = blockIdx.y, r0 = blockIdx.x * kExpertRows;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -621,8 +632,10 @@ __global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict
                 for (int u = 0; u < kExpertTile; ++u)
                     if (u == lane) { va = a[u]; vb = b[u]; }
                 const int entry = list[base + lane];
-                if (DUAL) reinterpret_cast<T*>(out_)[(size_t)entry * R + r] = from_f<T>(silu_f(va) * vb);
-                else reinterpret_cast<float*>(out_)[(size_t)entry * R + r] = wts[entry] * va;
+                const float wt = wts ? wts[entry] : 1.0f;
+                if (MODE == 1) reinterpret_cast<T*>(out_)[(size_t)entry * R + r] = from_f<T>(silu_f(wt * va) * (wt * vb));
+                else if (MODE == 2) { const float a2 = fmaxf(wt * va, 0.f); reinterpret_cast<T*>(out_)[(size_t)entry * R + r] = from_f<T>(a2 * a2); }
+                else reinterpret_cast<float*>(out_)[(size_t)entry * R + r] = wt * va;
             }
         }
     }
@@ -644,7 +657,7 @@ __global__ void weighted_scatter_kernel(const T* __restrict__ src, const int* __
                                         float* __restrict__ out, int width)
 {
     const int r = blockIdx.x, to = slot[r];
-    const float wt = wts[to];
+    const float wt = wts ? wts[to] : 1.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)to * width + i] = wt * to_f(src[(size_t)r * width + i]);
 }
 
@@ -674,6 +687,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int 
 }
 
 #include "window_attention.cuh"
+#include "ssm.cuh"
+#include "parallel_block.cuh"
 
 }  // namespace b200h
 
@@ -888,15 +903,32 @@ B200H_API int b200h_gated_rms(const void* o, const void* w, const void* gate, in
     return launched("gated_rms");
 }
 
-B200H_API int b200h_route(const void* x, const void* router, int n, int width, int experts, int top, void* ids, void* wts, void* stream)
+template <typename TI>
+static void launch_route(const void* x, const void* router, int n, int width, int experts, int top, int score_fn, void* ids, void* wts,
+                         size_t smem, cudaStream_t st)
 {
-    if (!x || !router || !ids || !wts || experts <= 0 || top <= 0 || top > experts) return fail(B200H_ERR_INVALID_ARG, "route: bad arguments");
+    if (smem > 48 * 1024) cudaFuncSetAttribute(route_kernel<TI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    route_kernel<TI><<<n, 256, smem, st>>>((const TI*)x, (const float*)router, width, experts, top, score_fn, (int*)ids, (float*)wts);
+}
+
+B200H_API int b200h_route_scored(const void* x, int x_dtype, const void* router, int n, int width, int experts, int top, int score_fn,
+                                 void* ids, void* wts, void* stream)
+{
+    if (!x || !router || !ids || !wts || experts <= 0 || top <= 0 || top > experts || score_fn < 0 || score_fn > 1)
+        return fail(B200H_ERR_INVALID_ARG, "route: bad arguments");
     if (n == 0) return 0;
     const size_t smem = (size_t)(width + experts) * sizeof(float);
     if (smem > 200 * 1024) return fail(B200H_ERR_UNSUPPORTED, "route: width + experts exceeds shared memory");
-    if (smem > 48 * 1024) cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    route_kernel<<<n, 256, smem, (cudaStream_t)stream>>>((const float*)x, (const float*)router, width, experts, top, (int*)ids, (float*)wts);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dtype == B200H_F32) launch_route<float>(x, router, n, width, experts, top, score_fn, ids, wts, smem, st);
+    else if (x_dtype == B200H_BF16) launch_route<bf16>(x, router, n, width, experts, top, score_fn, ids, wts, smem, st);
+    else return fail(B200H_ERR_UNSUPPORTED, "dtype: float32 (2) or bfloat16 (1)");
     return launched("route");
+}
+
+B200H_API int b200h_route(const void* x, const void* router, int n, int width, int experts, int top, void* ids, void* wts, void* stream)
+{
+    return b200h_route_scored(x, B200H_F32, router, n, width, experts, top, 0, ids, wts, stream);
 }
 
 template <typename T>
@@ -906,27 +938,32 @@ static void launch_expert_rows(const b200h_expert_args* a, cudaStream_t st)
     const bool vec = a->width % Pack<T>::N == 0 && a->ff % Pack<T>::N == 0;
     const size_t sm_up = (size_t)kExpertTile * a->width * sizeof(T), sm_down = (size_t)kExpertTile * a->ff * sizeof(T);
     const dim3 g_up((a->ff + kExpertRows - 1) / kExpertRows, a->experts), g_down((a->width + kExpertRows - 1) / kExpertRows, a->experts);
-#define B200H_ROWS(DUAL, VEC, GRID, SM, X, DIV, WA, WB, K, R, OUT)                                                                      \
+    // the router's score goes to the first product when it scales the expert's input, to the last one otherwise
+    const float* w_in = a->scale_input ? (const float*)a->wts : nullptr;
+    const float* w_out = a->scale_input ? nullptr : (const float*)a->wts;
+#define B200H_ROWS(MODE, VEC, GRID, SM, X, DIV, WA, WB, WTS, K, R, OUT)                                                                 \
     do {                                                                                                                               \
         if ((SM) > 48 * 1024)                                                                                                          \
-            cudaFuncSetAttribute(expert_rows_kernel<T, DUAL, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SM));            \
-        expert_rows_kernel<T, DUAL, VEC><<<GRID, 256, SM, st>>>((const T*)(X), DIV, (const T*)(WA), (const T*)(WB), (const int*)a->counts, \
-                                                               (const int*)a->lists, entries, (const float*)a->wts, K, R, OUT);         \
+            cudaFuncSetAttribute(expert_rows_kernel<T, MODE, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SM));            \
+        expert_rows_kernel<T, MODE, VEC><<<GRID, 256, SM, st>>>((const T*)(X), DIV, (const T*)(WA), (const T*)(WB), (const int*)a->counts, \
+                                                               (const int*)a->lists, entries, WTS, K, R, OUT);                          \
     } while (0)
-    if (vec) {
-        B200H_ROWS(true, true, g_up, sm_up, a->x, a->top, a->gate, a->up, a->width, a->ff, a->mid);
-        B200H_ROWS(false, true, g_down, sm_down, a->mid, 1, a->down, nullptr, a->ff, a->width, a->out);
+    if (a->act == 1) {
+        if (vec) B200H_ROWS(2, true, g_up, sm_up, a->x, a->top, a->up, nullptr, w_in, a->width, a->ff, a->mid);
+        else B200H_ROWS(2, false, g_up, sm_up, a->x, a->top, a->up, nullptr, w_in, a->width, a->ff, a->mid);
     } else {
-        B200H_ROWS(true, false, g_up, sm_up, a->x, a->top, a->gate, a->up, a->width, a->ff, a->mid);
-        B200H_ROWS(false, false, g_down, sm_down, a->mid, 1, a->down, nullptr, a->ff, a->width, a->out);
+        if (vec) B200H_ROWS(1, true, g_up, sm_up, a->x, a->top, a->gate, a->up, w_in, a->width, a->ff, a->mid);
+        else B200H_ROWS(1, false, g_up, sm_up, a->x, a->top, a->gate, a->up, w_in, a->width, a->ff, a->mid);
     }
+    if (vec) B200H_ROWS(0, true, g_down, sm_down, a->mid, 1, a->down, nullptr, w_out, a->ff, a->width, a->out);
+    else B200H_ROWS(0, false, g_down, sm_down, a->mid, 1, a->down, nullptr, w_out, a->ff, a->width, a->out);
 #undef B200H_ROWS
 }
 
 B200H_API int b200h_experts(const b200h_expert_args* a)
 {
-    if (!a || !a->x || !a->gate || !a->up || !a->down || !a->ids || !a->wts || !a->out || !a->mid || !a->counts || !a->lists ||
-        a->ff <= 0 || a->experts <= 0 || a->top <= 0)
+    if (!a || !a->x || !a->up || !a->down || !a->ids || !a->wts || !a->out || !a->mid || !a->counts || !a->lists ||
+        a->ff <= 0 || a->experts <= 0 || a->top <= 0 || a->act < 0 || a->act > 1 || (a->act == 0 && !a->gate))
         return fail(B200H_ERR_INVALID_ARG, "experts: bad arguments");
     if (a->n == 0) return 0;
     const size_t widest = (size_t)kExpertTile * (a->width > a->ff ? a->width : a->ff) * (a->dtype == B200H_F32 ? 4 : 2);
@@ -951,7 +988,7 @@ B200H_API int b200h_silu_mul(const void* g, const void* u, void* out, int64_t co
 B200H_API int b200h_weighted_scatter(const void* src, const void* slot, const void* wts, void* out, int rows, int width, int dtype,
                                      void* stream)
 {
-    if (!src || !slot || !wts || !out || width <= 0) return fail(B200H_ERR_INVALID_ARG, "weighted_scatter: bad arguments");
+    if (!src || !slot || !out || width <= 0) return fail(B200H_ERR_INVALID_ARG, "weighted_scatter: bad arguments");
     if (rows == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     B200H_DISPATCH_T(dtype, weighted_scatter_kernel<T><<<rows, 256, 0, st>>>((const T*)src, (const int*)slot, (const float*)wts, (float*)out,
@@ -1088,7 +1125,7 @@ B200H_API int b200h_window_attention(const b200h_window_args* a)
     g.n = a->n; g.rows = 1; g.tile = 32;
     g.heads = a->heads; g.kv_heads = a->kv_heads; g.dim = a->dim; g.vdim = a->vdim; g.block_len = a->block_len;
     g.window = a->window; g.splits = a->splits; g.scale = a->scale; g.softcap = a->softcap;
-    g.r1 = (const float*)a->r1; g.r2 = (const float*)a->r2; g.talk = (const float*)a->talk;
+    g.r1 = (const float*)a->r1; g.r2 = (const float*)a->r2; g.talk = (const float*)a->talk; g.sink = (const float*)a->sink;
     g.tok_seq = (const int*)a->tok_seq; g.tok_pos = (const int*)a->tok_pos;
     g.block_ptrs = (const int64_t*)a->block_ptrs; g.cu_blocks = (const int*)a->cu_blocks;
     g.layer_off = a->layer_off; g.v_off = a->v_off;
@@ -1105,4 +1142,119 @@ B200H_API int b200h_window_attention(const b200h_window_args* a)
     else { B200H_DISPATCH_T(a->dtype, rc = (launch_window_attention<T, false, 1>(a, g, st))); }
     if (rc) return rc;
     return launched("window_attention");
+}
+
+
+// ------------------------------------------------------------------------------------------------ parallel blocks, state-space mixer
+B200H_API int b200h_parallel_residual_norm(void* x, const void* mix, const void* ff, int parts, float mult, const void* add, const void* extra,
+                                           const void* w1, const void* w2, int n, int width, float eps, void* h1, void* h2, int dtype,
+                                           void* stream)
+{
+    if (!x || n < 0 || width <= 0 || (h1 && !w1) || (h2 && !w2) || (ff && parts < 1))
+        return fail(B200H_ERR_INVALID_ARG, "parallel_residual_norm: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, parallel_residual_norm_kernel<T><<<n, 256, 0, st>>>((float*)x, (const T*)mix, (const float*)ff, ff ? parts : 0, mult,
+                                                                               (const float*)add, (const T*)extra, (const float*)w1,
+                                                                               (const float*)w2, width, eps, (T*)h1, (T*)h2));
+    return launched("parallel_residual_norm");
+}
+
+B200H_API int b200h_short_conv(const void* u, int64_t ld, const void* w, const void* bias, int act, void* state, int64_t slot_stride,
+                               const void* tok_seq, const void* cu_q, const void* seq_slot, void* out, int n, int batch, int channels,
+                               int taps, int dtype, void* stream)
+{
+    if (!u || !w || !state || !tok_seq || !cu_q || !seq_slot || !out || channels <= 0 || batch <= 0 || act < 0 || act > 1)
+        return fail(B200H_ERR_INVALID_ARG, "short_conv: bad arguments");
+    if (taps < 1 || taps > B200H_MAX_TAPS) return fail(B200H_ERR_UNSUPPORTED, "short_conv: taps 1..16");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const dim3 grid(n, (channels + 1023) / 1024), sgrid((channels + 255) / 256, batch);
+    B200H_DISPATCH_T(dtype, {
+        short_conv_kernel<T><<<grid, 256, 0, st>>>((const T*)u, ld, (const float*)w, (const float*)bias, act, (const float*)state, slot_stride,
+                                                   (const int*)tok_seq, (const int*)cu_q, (const int*)seq_slot, (float*)out, channels, taps);
+        if (taps > 1)
+            short_conv_state_kernel<T><<<sgrid, 256, 0, st>>>((const T*)u, ld, (float*)state, slot_stride, (const int*)cu_q, (const int*)seq_slot,
+                                                            channels, taps);
+    });
+    return launched("short_conv");
+}
+
+B200H_API int b200h_ssm_scan(const void* xbc, const void* dt, int64_t ld_dt, const void* dt_bias, const void* a_log, const void* skip,
+                             void* state, int64_t slot_stride, const void* cu_q, const void* seq_slot, int batch, int heads, int vdim,
+                             int nstate, int groups, void* out, int dtype, void* stream)
+{
+    if (!xbc || !dt || !dt_bias || !a_log || !skip || !state || !cu_q || !seq_slot || !out || batch <= 0 || heads <= 0 || vdim <= 0 ||
+        nstate <= 0 || groups <= 0 || heads % groups)
+        return fail(B200H_ERR_INVALID_ARG, "ssm_scan: bad arguments");
+    if (nstate > 256) return fail(B200H_ERR_UNSUPPORTED, "ssm_scan: state <= 256");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int cols = vdim < 8 ? vdim : 8;
+    const dim3 grid((vdim + cols - 1) / cols, heads, batch), block(32, cols);
+    const int nw = (nstate + 31) / 32;
+#define B200H_SCAN(NW)                                                                                                                   \
+    ssm_scan_kernel<T, NW><<<grid, block, 0, st>>>((const float*)xbc, (const T*)dt, ld_dt, (const float*)dt_bias, (const float*)a_log,    \
+                                                   (const float*)skip, (float*)state, slot_stride, (const int*)cu_q, (const int*)seq_slot, \
+                                                   heads, vdim, nstate, groups, (float*)out)
+    B200H_DISPATCH_T(dtype, if (nw <= 1) B200H_SCAN(1); else if (nw <= 2) B200H_SCAN(2); else if (nw <= 4) B200H_SCAN(4); else B200H_SCAN(8));
+#undef B200H_SCAN
+    return launched("ssm_scan");
+}
+
+B200H_API int b200h_gate_group_norm(const void* y, const void* gate, int64_t ld_gate, const void* w, int n, int count, int groups, float eps,
+                                    void* out, int dtype, void* stream)
+{
+    if (!y || !gate || !w || !out || count <= 0 || groups <= 0 || count % groups) return fail(B200H_ERR_INVALID_ARG, "gate_group_norm: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, gate_group_norm_kernel<T><<<dim3(n, groups), 256, 0, st>>>((const float*)y, (const T*)gate, ld_gate, (const float*)w,
+                                                                                      count, groups, eps, (T*)out));
+    return launched("gate_group_norm");
+}
+
+B200H_API int b200h_conv_rope_prep(const b200h_conv_prep_args* a)
+{
+    if (!a || !a->qk || !a->conv || !a->state || !a->qn || !a->tok_seq || !a->tok_pos || !a->cu_q || !a->seq_slot || !a->block_ptrs ||
+        !a->cu_blocks || a->heads <= 0 || a->kv_heads <= 0 || a->dim <= 0 || a->dim % 2 || a->block_len <= 0 || a->batch <= 0)
+        return fail(B200H_ERR_INVALID_ARG, "conv_rope_prep: bad arguments");
+    if (a->taps < 1 || a->taps > B200H_MAX_TAPS) return fail(B200H_ERR_UNSUPPORTED, "conv_rope_prep: taps 1..16");
+    if (a->rot.pairs < 0 || 2 * a->rot.pairs > a->dim || (a->rot.pairs && !a->rot.freqs))
+        return fail(B200H_ERR_INVALID_ARG, "conv_rope_prep: rotated pairs do not fit a head");
+    if (a->n == 0) return 0;
+    const int channels = (a->heads + a->kv_heads) * a->dim;
+    const size_t smem = (size_t)(channels + 2 * a->rot.pairs) * sizeof(float);
+    if (smem > 200 * 1024) return fail(B200H_ERR_UNSUPPORTED, "conv_rope_prep: (heads + kv_heads) * dim floats exceed shared memory");
+    cudaStream_t st = (cudaStream_t)a->stream;
+    const Rotary rot = make_rotary(&a->rot);
+    const dim3 sgrid((channels + 255) / 256, a->batch);
+    B200H_DISPATCH_T(a->dtype, {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(conv_rope_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        conv_rope_prep_kernel<T><<<a->n, 256, smem, st>>>((const T*)a->qk, a->ld, (const float*)a->conv, a->taps, (const float*)a->state,
+                                                          a->slot_stride, (const int*)a->tok_seq, (const int*)a->tok_pos, (const int*)a->cu_q,
+                                                          (const int*)a->seq_slot, rot, a->heads, a->kv_heads, a->dim, a->eps,
+                                                          (const int64_t*)a->block_ptrs, (const int*)a->cu_blocks, a->layer_off, a->v_off,
+                                                          a->block_len, (float*)a->qn);
+        if (a->taps > 1)
+            short_conv_state_kernel<T><<<sgrid, 256, 0, st>>>((const T*)a->qk, a->ld, (float*)a->state, a->slot_stride, (const int*)a->cu_q,
+                                                            (const int*)a->seq_slot, channels, a->taps);
+    });
+    return launched("conv_rope_prep");
+}
+
+B200H_API int b200h_softcap(void* x, int64_t count, float cap, void* stream)
+{
+    if (!x || count < 0 || !(cap > 0.f)) return fail(B200H_ERR_INVALID_ARG, "softcap: bad arguments");
+    if (count == 0) return 0;
+    softcap_kernel<<<(unsigned)((count + 255) / 256), 256, 0, (cudaStream_t)stream>>>((float*)x, count, cap);
+    return launched("softcap");
+}
+
+B200H_API int b200h_scaled_relu2(void* u, const void* scale, int rows, int cols, int dtype, void* stream)
+{
+    if (!u || rows < 0 || cols <= 0) return fail(B200H_ERR_INVALID_ARG, "scaled_relu2: bad arguments");
+    if (rows == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t count = (int64_t)rows * cols;
+    B200H_DISPATCH_T(dtype, scaled_relu2_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, st>>>((T*)u, (const float*)scale, cols, count));
+    return launched("scaled_relu2");
 }

@@ -116,6 +116,7 @@ struct WindowGeom {
     const float* r1;          // [heads] or nullptr: no distance penalty
     const float* r2;
     const float* talk;        // [heads, heads] or nullptr: heads are not recombined
+    const float* sink;        // [heads] or nullptr: a score per head that joins the softmax denominator and carries no value
     const int* tok_seq;
     const int* tok_pos;
     const int64_t* block_ptrs;
@@ -345,6 +346,7 @@ __global__ void __launch_bounds__(256) window_pv_kernel(WindowGeom g, const floa
             const float* src = ml + ((size_t)ta * H + i) * g.splits * 2;
             float mm = src[0], ll = src[1];
             for (int k = 1; k < g.splits; ++k) merge_ml(mm, ll, src[2 * k], src[2 * k + 1]);
+            if (g.sink) merge_ml(mm, ll, g.sink[i % H], 1.0f);
             mx[i] = mm;
             linv[i] = 1.0f / ll;
         }

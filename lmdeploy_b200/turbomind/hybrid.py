@@ -3,10 +3,11 @@
 A hybrid decoder mixes layer kinds, so a sequence owns two things between steps:
   * pages of the engine's block pool (runtime.KvCachePool, handed out by scheduler.BlockAllocator) -- every latent-attention
     layer keeps, per position, its normed key/value latent (as T) and the rotated key part all heads share (as float); every
-    windowed-attention layer its normed keys and its values (as T);
+    windowed-attention or convolved-rotary-attention layer its normed keys and its values (as T);
   * one slot of the StatePool (handed out by scheduler.Scheduler's slot list) -- per layer the last taps-1 inputs of the
-    short convolution (of both sublayers in pre-norm blocks), and per decayed-linear-attention layer the [heads, vdim, dim]
-    float state.
+    short convolution (of both sublayers in pre-norm blocks; of the stacked q | k projection of a convolved attention; of the
+    x | B | C channels of a state-space mixer), per decayed-linear-attention layer the [heads, vdim, dim] float state and per
+    state-space layer the [heads, vdim, state] float state.
 A layer that a spec loops (HybridSpec.loop) is executed several times per step with the same weights: caches and states
 belong to RUNS (HybridSpec.runs()), weights to layers.
 The step is a mixed step like b200_model_chunk_step: any number of rows per sequence, prompt portions beside single decoded
@@ -79,7 +80,7 @@ class HybridModel:
         # state slot: per run [taps-1, width] conv inputs (twice where the feed-forward has a conv too), then per decay layer [heads, vdim, dim]
         self.cache_off, self.rot_off, self.conv_off, self.mix_off, self.conv2_off, self.v_off = {}, {}, {}, {}, {}, {}
         self.runs = spec.runs()
-        if spec.block not in ("post_norm", "pre_norm"):
+        if spec.block not in ("post_norm", "pre_norm", "parallel"):
             raise NotImplementedError(f"block {spec.block!r}")
         pre = spec.block == "pre_norm"
         page = slot = 0
@@ -87,12 +88,33 @@ class HybridModel:
         for r, (i, _) in enumerate(self.runs):
             layer = spec.layers[i]
             m = layer.mixer
-            self.conv_off[r] = slot
-            slot += (taps - 1) * spec.width
+            self.conv_off[r] = slot             # parallel blocks have no convolution on the stream: the mixers bring their own
+            if spec.block != "parallel":
+                slot += (taps - 1) * spec.width
             if pre and layer.mlp is not None:
                 self.conv2_off[r] = slot
                 slot += (taps - 1) * spec.width
-            if m.kind == "latent_attention":
+            if m.kind == "conv_attention":
+                if not 1 <= m.conv_taps <= H.MAX_TAPS:
+                    raise NotImplementedError(f"conv taps {m.conv_taps} (1..{H.MAX_TAPS})")
+                if not m.values_from_keys:
+                    raise NotImplementedError("convolved attention with a value projection of its own")
+                # state: the last taps-1 rows of the stacked q | k projection; cache region as for windowed attention
+                self.conv_off[r] = slot
+                slot += (m.conv_taps - 1) * (m.heads + m.kv_heads) * m.dim
+                self.cache_off[r] = page
+                self.v_off[r] = _align(block_len * m.kv_heads * m.dim * esize)
+                page += self.v_off[r] + _align(block_len * m.kv_heads * m.vdim * esize)
+            elif m.kind == "mamba2":
+                if not 1 <= m.conv_taps <= H.MAX_TAPS:
+                    raise NotImplementedError(f"conv taps {m.conv_taps} (1..{H.MAX_TAPS})")
+                if m.state > 256:
+                    raise NotImplementedError("state-space mixer: state <= 256")
+                self.conv_off[r] = slot
+                slot += (m.conv_taps - 1) * m.conv_channels
+                self.mix_off[r] = slot
+                slot += m.heads * m.vdim * m.state
+            elif m.kind == "latent_attention":
                 if m.kv_rank > 512 or m.rot_dim > 128:
                     raise NotImplementedError("latent attention: kv_rank <= 512 and rot_dim <= 128")
                 self.cache_off[r] = page
@@ -157,14 +179,15 @@ class HybridModel:
 
         W = s.width
         pre = s.block == "pre_norm"
+        par = s.block == "parallel"
 
         def norm_w(name):
-            # pre-norm blocks store a norm weight as its deviation from one: the kernels get the full factor
+            # pre-norm and parallel blocks store a norm weight as its deviation from one: the kernels get the full factor
             t = f32(name, (W,))
-            return t + 1.0 if pre else t
+            return t + 1.0 if pre or par else t
 
         w["embed"] = lin("embed", shape=(s.vocab, W))
-        w["head"] = lin("head", shape=(s.vocab, W))
+        w["head"] = w["embed"] if s.tied_head else lin("head", shape=(s.vocab, W))
         w["final.norm"] = norm_w("final.norm")
         if s.max_positions:
             w["pos"] = lin("pos", shape=(s.max_positions, W))
@@ -173,10 +196,29 @@ class HybridModel:
         for i, layer in enumerate(s.layers):
             p, m = f"l{i}.", layer.mixer
             w[p + "norm1"] = norm_w(p + "norm1")
-            w[p + "canon1"] = f32(p + "canon1", (W, s.conv_taps))
-            if not pre:
+            if not par:
+                w[p + "canon1"] = f32(p + "canon1", (W, s.conv_taps))
+            if s.block == "post_norm":
                 w[p + "dwa"] = f32(p + "dwa", (i + 2,))
-            if m.kind == "latent_attention":
+            if m.kind == "conv_attention":
+                HD, GD = m.heads * m.dim, m.kv_heads * m.dim
+                w[p + "in"] = lin(p + "mix.q", p + "mix.k", shape=(HD + GD, W))
+                w[p + "conv"] = torch.cat([f32(p + "mix.q.conv", (HD, m.conv_taps)), f32(p + "mix.k.conv", (GD, m.conv_taps))]).contiguous()
+                w[p + "o"] = lin(p + "mix.o", shape=(W, m.heads * m.vdim))
+                freqs, mag = m.rot.frequencies()
+                w[p + "freqs"] = torch.tensor(freqs, dtype=torch.float64, device=dev)
+                w[p + "mag"] = float(mag)
+                if m.sink is not None:
+                    w[p + "sink"] = torch.full((m.heads,), float(m.sink), dtype=torch.float32, device=dev)
+            elif m.kind == "mamba2":
+                w[p + "in"] = lin(p + "mix.in", shape=(m.proj_cols, W))
+                w[p + "conv"] = f32(p + "mix.conv", (m.conv_channels, m.conv_taps))
+                w[p + "conv.b"] = f32(p + "mix.conv.b", (m.conv_channels,))
+                for k in ("dt_bias", "A_log", "D"):
+                    w[p + k] = f32(p + "mix." + k, (m.heads,))
+                w[p + "mixnorm"] = f32(p + "mix.norm", (m.inner,))
+                w[p + "o"] = lin(p + "mix.o", shape=(W, m.inner))
+            elif m.kind == "latent_attention":
                 HV = m.heads * m.vdim
                 w[p + "in"] = lin(p + "mix.dq", p + "mix.dkv", p + "mix.g", shape=(m.q_rank + m.kv_rank + m.rot_dim + HV, W))
                 w[p + "uq"] = lin(p + "mix.uq", shape=(m.heads * (m.dim + m.rot_dim), m.q_rank))
@@ -221,6 +263,8 @@ class HybridModel:
                     continue
                 w[p + "router"] = f32(p + "mlp.router", (f.experts, W))
                 for part, shape in (("gate", (f.ff, W)), ("up", (f.ff, W)), ("down", (W, f.ff))):
+                    if part == "gate" and f.act != "silu_gate":
+                        continue
                     w[p + part] = torch.stack([lin(f"{p}mlp.e{e}.{part}", shape=shape) for e in range(f.experts)]).contiguous()
         if dev.type == "cuda":
             torch.cuda.synchronize(dev)
@@ -232,8 +276,16 @@ class HybridModel:
 
         def get(name):
             shape = self.tensor_shapes()[name]
-            if name.endswith(("norm1", "norm2", "final.norm")) and self.spec.block == "pre_norm":
+            if name.endswith(("norm1", "norm2", "final.norm")) and self.spec.block in ("pre_norm", "parallel"):
                 return 0.1 * torch.randn(shape, generator=g)            # stored as the deviation from one
+            if name.endswith((".conv", ".conv.b")):
+                return torch.randn(shape, generator=g) / (shape[-1] if name.endswith(".conv") else 10.0)
+            if name.endswith(".A_log"):
+                return torch.log(1.0 + 15.0 * torch.rand(shape, generator=g))
+            if name.endswith(".dt_bias"):
+                return torch.log(torch.expm1(0.001 + 0.099 * torch.rand(shape, generator=g)))
+            if name.endswith(".D"):
+                return torch.ones(shape)
             if name.endswith(("norm1", "norm2", ".norm")):
                 return 1.0 + 0.1 * torch.randn(shape, generator=g)
             if name.endswith(("canon1", "canon2")):
@@ -257,17 +309,30 @@ class HybridModel:
         """Checkpoint tensor names -> shapes for this spec."""
         s, W = self.spec, self.spec.width
         pre = s.block == "pre_norm"
-        out = {"embed": (s.vocab, W), "head": (s.vocab, W), "final.norm": (W,)}
+        par = s.block == "parallel"
+        out = {"embed": (s.vocab, W), "final.norm": (W,)}
+        if not s.tied_head:
+            out["head"] = (s.vocab, W)
         if s.max_positions:
             out["pos"] = (s.max_positions, W)
         if s.loop is not None:
             out["loop.step"] = (s.loop[2], W)
         for i, layer in enumerate(s.layers):
             p, m = f"l{i}.", layer.mixer
-            out.update({p + "norm1": (W,), p + "canon1": (W, s.conv_taps)})
-            if not pre:
+            out[p + "norm1"] = (W,)
+            if not par:
+                out[p + "canon1"] = (W, s.conv_taps)
+            if s.block == "post_norm":
                 out[p + "dwa"] = (i + 2,)
-            if m.kind == "latent_attention":
+            if m.kind == "conv_attention":
+                HD, GD = m.heads * m.dim, m.kv_heads * m.dim
+                out.update({p + "mix.q": (HD, W), p + "mix.k": (GD, W), p + "mix.q.conv": (HD, m.conv_taps), p + "mix.k.conv": (GD, m.conv_taps),
+                            p + "mix.o": (W, m.heads * m.vdim)})
+            elif m.kind == "mamba2":
+                out.update({p + "mix.in": (m.proj_cols, W), p + "mix.conv": (m.conv_channels, m.conv_taps), p + "mix.conv.b": (m.conv_channels,),
+                            p + "mix.dt_bias": (m.heads,), p + "mix.A_log": (m.heads,), p + "mix.D": (m.heads,), p + "mix.norm": (m.inner,),
+                            p + "mix.o": (W, m.inner)})
+            elif m.kind == "latent_attention":
                 HV = m.heads * m.vdim
                 out.update({p + "mix.dq": (m.q_rank, W), p + "mix.dq.norm": (m.q_rank,), p + "mix.uq": (m.heads * (m.dim + m.rot_dim), m.q_rank),
                             p + "mix.dkv": (m.kv_rank + m.rot_dim, W), p + "mix.dkv.norm": (m.kv_rank,),
@@ -300,7 +365,9 @@ class HybridModel:
                     continue
                 out[p + "mlp.router"] = (f.experts, W)
                 for e in range(f.experts):
-                    out.update({f"{p}mlp.e{e}.gate": (f.ff, W), f"{p}mlp.e{e}.up": (f.ff, W), f"{p}mlp.e{e}.down": (W, f.ff)})
+                    out.update({f"{p}mlp.e{e}.up": (f.ff, W), f"{p}mlp.e{e}.down": (W, f.ff)})
+                    if f.act == "silu_gate":
+                        out[f"{p}mlp.e{e}.gate"] = (f.ff, W)
         return out
 
     # ------------------------------------------------------------------ step
@@ -342,6 +409,10 @@ class HybridModel:
         st = self._stream()
         if s.max_positions and max_pos >= s.max_positions:
             raise ValueError(f"position {max_pos}: the model has {s.max_positions} learned positions")
+        if s.block == "parallel":
+            return self._step_parallel(n=n, batch=batch, tokens=tokens, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot,
+                                       block_ptrs=block_ptrs, cu_blocks=cu_blocks, state=state, rows=rows, n_rows=n_rows, max_pos=max_pos,
+                                       trace=trace)
         if s.block == "pre_norm":
             return self._step_pre_norm(n=n, batch=batch, tokens=tokens, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot,
                                        block_ptrs=block_ptrs, cu_blocks=cu_blocks, state=state, rows=rows, n_rows=n_rows, max_pos=max_pos,
@@ -421,6 +492,60 @@ class HybridModel:
                                               dt, st), "group_norm_rows")
             return self._logits(xn)
 
+    def _step_parallel(self, *, n, batch, tokens, tok_seq, tok_pos, cu_q, seq_slot, block_ptrs, cu_blocks, state, rows, n_rows, max_pos,
+                       trace=None):
+        """The step of parallel blocks: x <- x + mult * (mixer(n1(x)) + ff(n2(x))) per run, both sublayers reading the same stream.
+        One kernel per run takes the previous run's two outputs into the float stream (and, before a pass of looped layers, the
+        embedding output and the pass's vector) and emits both normed inputs of this run."""
+        s, lib, w, dev, T, dt = self.spec, self.lib, self.w, self.device, self.T, self.dt
+        W, eps, st = s.width, s.norm_eps, self._stream()
+        c = StepArrays(n=n, batch=batch, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot, block_ptrs=block_ptrs,
+                       cu_blocks=cu_blocks, state=state, max_pos=max_pos)
+        x = torch.empty(n, W, dtype=torch.float32, device=dev)
+        with self.timed("embed"):
+            H.check(lib.b200h_embed(tokens.data_ptr(), w["embed"].data_ptr(), s.embedding_scale, x.data_ptr(), n, W, dt, st), "embed")
+            e0 = x.clone() if s.loop is not None and s.loop_readds_embedding and s.loop[2] > 1 else None
+        h1 = torch.empty(n, W, dtype=T, device=dev)
+        h2 = torch.empty(n, W, dtype=T, device=dev)
+        mix = ff = None                  # the previous run's outputs that the stream has not taken in yet
+        parts = 0
+
+        def join(add, extra, w1, w2):
+            with self.timed("residual + two norms"):
+                H.check(lib.b200h_parallel_residual_norm(
+                    x.data_ptr(), None if mix is None else mix.data_ptr(), None if ff is None else ff.data_ptr(), parts, s.residual_mult,
+                    add, extra, None if w1 is None else w1.data_ptr(), None if w2 is None else w2.data_ptr(), n, W, eps,
+                    None if w1 is None else h1.data_ptr(), None if w2 is None else h2.data_ptr(), dt, st), "parallel_residual_norm")
+
+        for r, (i, t) in enumerate(self.runs):
+            p, layer = f"l{i}.", s.layers[i]
+            add = extra = None
+            if t is not None and i == s.loop[0]:
+                if t > 0 and e0 is not None:
+                    add = e0.data_ptr()
+                extra = w["loop.step"].data_ptr() + t * W * w["loop.step"].element_size()
+            f = layer.mlp
+            join(add, extra, w[p + "norm1"], w[p + "norm2"] if f is not None else None)
+            y = self.mixer(r, i, h1, c)
+            with self.timed("gemm out"):
+                mix = self._linear(y, w[p + "o"])
+            ff, parts = None, 0
+            if f is not None:
+                if f.kind != "moe":
+                    raise NotImplementedError(f"parallel blocks with a {f.kind!r} feed-forward")
+                ff, parts = self.routed_experts(i, None, h2, n), f.top
+            if trace is not None:
+                join(None, None, None, None)
+                mix = ff = None
+                trace.append(x.clone())
+        xn = torch.empty(n_rows, W, dtype=T, device=dev)
+        with self.timed("final norm + head"):
+            if mix is not None or ff is not None:
+                join(None, None, None, None)
+            H.check(lib.b200h_group_norm_rows(x.data_ptr(), rows.data_ptr(), w["final.norm"].data_ptr(), n_rows, W, 1, eps, xn.data_ptr(),
+                                              dt, st), "group_norm_rows")
+            return self._logits(xn)
+
     def norm_conv_input(self, r, i, sub, x, pending, extra, c):
         """What sublayer `sub` (1: mixer, 2: feed-forward) of run r reads: first the stream takes in `pending` (the previous
         sublayer's output) and `extra` (a vector for all rows), then h = norm(x), then h + causal convolution of h over the
@@ -440,6 +565,10 @@ class HybridModel:
             return self.latent_mixer(i, h, c, run=r)
         if kind == "window_attention":
             return self.window_mixer(i, h, c, run=r)
+        if kind == "conv_attention":
+            return self.conv_attention_mixer(i, h, c, run=r)
+        if kind == "mamba2":
+            return self.ssm_mixer(i, h, c, run=r)
         return self.decay_mixer(i, h, c, run=r)
 
     def window_splits(self, n, window, max_pos):
@@ -496,8 +625,16 @@ class HybridModel:
         a.layer_off, a.v_off, a.dtype, a.stream = self.cache_off[r], self.v_off[r], self.dt, self._stream()
         with self.timed("qk norm + cache store"):
             H.check(lib.b200h_window_prep(C.byref(a)), "window_prep")
-        # pass 1 leaves every row's scores in a scratch [rows, heads, keys a row can see] for pass 2; the step's rows go through
-        # the two passes in chunks that keep the scratch within `window_scratch_bytes`
+        self._window_attend(a, m, c, qn, y, "windowed attention")
+        return y
+
+    def _window_attend(self, a, m, c, qn, y, name):
+        """The two attention passes over the cache for a prepared step (a: WindowArgs with sizes, switches, cache offsets and, if any,
+        gate filled in; qn float [n, heads * dim]; y T [n, heads * vdim]).  Pass 1 leaves every row's scores in a scratch [rows,
+        heads, keys a row can see] for pass 2; the step's rows go through the two passes in chunks that keep the scratch within
+        `window_scratch_bytes`."""
+        n, HD, HV, es = c.n, m.heads * m.dim, m.heads * m.vdim, y.element_size()
+        f32 = dict(dtype=torch.float32, device=self.device)
         a.score_ld = self.window_score_ld(m.window, c.max_pos)
         chunk = max(4, self.window_scratch_bytes // (4 * m.heads * a.score_ld) // 4 * 4)
         rows = min(n, chunk)
@@ -505,15 +642,79 @@ class HybridModel:
         ml = torch.empty(rows, m.heads, a.splits, 2, **f32)
         o_part = torch.empty(rows, a.splits, HV, **f32)
         a.scores, a.ml, a.o_part = scores.data_ptr(), ml.data_ptr(), o_part.data_ptr()
-        gate = a.gate
-        with self.timed("windowed attention"):
+        gate, ld_gate = a.gate, a.ld_gate
+        with self.timed(name):
             for at in range(0, n, chunk):
                 a.n = min(chunk, n - at)
                 a.qn, a.y = qn.data_ptr() + 4 * at * HD, y.data_ptr() + es * at * HV
                 a.tok_seq, a.tok_pos = c.tok_seq.data_ptr() + 4 * at, c.tok_pos.data_ptr() + 4 * at
-                if m.gate:
-                    a.gate = gate + es * at * ld
-                H.check(lib.b200h_window_attention(C.byref(a)), "window_attention")
+                if gate:
+                    a.gate = gate + es * at * ld_gate
+                H.check(self.lib.b200h_window_attention(C.byref(a)), "window_attention")
+
+    def conv_attention_mixer(self, i, h, c, run=None):
+        """Convolved rotary attention of layer i: one stacked projection (q | k); one kernel convolves every channel over the
+        sequence (state: the last taps-1 projected rows), stores the convolved key as the VALUE, rotates, norms per head and stores
+        the key; then attention over all cached keys with the sink in the denominator.  Returns [n, heads * vdim] (T)."""
+        r = i if run is None else run
+        m, w, lib, dev, T, n = self.spec.layers[i].mixer, self.w, self.lib, self.device, self.T, c.n
+        p = f"l{i}."
+        HD, HV = m.heads * m.dim, m.heads * m.vdim
+        with self.timed("gemm in"):
+            proj = self._linear(h, w[p + "in"])
+        qn = torch.empty(n, HD, dtype=torch.float32, device=dev)
+        pa = H.ConvPrepArgs()
+        pa.n, pa.batch, pa.heads, pa.kv_heads, pa.dim, pa.taps, pa.block_len = n, c.batch, m.heads, m.kv_heads, m.dim, m.conv_taps, self.block_len
+        pa.eps = self.spec.norm_eps
+        pa.rot = H.Rotary(w[p + "freqs"].data_ptr(), m.rot.dims // 2, w[p + "mag"])
+        pa.qk, pa.ld, pa.conv = proj.data_ptr(), proj.stride(0), w[p + "conv"].data_ptr()
+        pa.state, pa.slot_stride, pa.qn = c.state.ptr(self.conv_off[r]), c.state.storage.stride(0), qn.data_ptr()
+        pa.tok_seq, pa.tok_pos, pa.cu_q, pa.seq_slot = c.tok_seq.data_ptr(), c.tok_pos.data_ptr(), c.cu_q.data_ptr(), c.seq_slot.data_ptr()
+        pa.block_ptrs, pa.cu_blocks = c.block_ptrs.data_ptr(), c.cu_blocks.data_ptr()
+        pa.layer_off, pa.v_off, pa.dtype, pa.stream = self.cache_off[r], self.v_off[r], self.dt, self._stream()
+        with self.timed("conv + rotate + head norm + cache store"):
+            H.check(lib.b200h_conv_rope_prep(C.byref(pa)), "conv_rope_prep")
+        a = H.WindowArgs()
+        a.n, a.heads, a.kv_heads, a.dim, a.vdim, a.block_len, a.window = n, m.heads, m.kv_heads, m.dim, m.vdim, self.block_len, m.window
+        a.splits = self.window_splits(n, m.window, c.max_pos)
+        a.scale, a.softcap, a.eps = m.scale, 0.0, self.spec.norm_eps
+        if m.sink is not None:
+            a.sink = w[p + "sink"].data_ptr()
+        a.qn = qn.data_ptr()
+        a.tok_seq, a.tok_pos = c.tok_seq.data_ptr(), c.tok_pos.data_ptr()
+        a.block_ptrs, a.cu_blocks = c.block_ptrs.data_ptr(), c.cu_blocks.data_ptr()
+        a.layer_off, a.v_off, a.dtype, a.stream = self.cache_off[r], self.v_off[r], self.dt, self._stream()
+        y = torch.empty(n, HV, dtype=T, device=dev)
+        self._window_attend(a, m, c, qn, y, "attention with sink")
+        return y
+
+    def ssm_mixer(self, i, h, c, run=None):
+        """State-space mixer of layer i: one projection (z | x | B | C | dt), the short convolution with bias and silu over
+        x | B | C (float out), the per-head recurrence on the sequence's float state, then the gate silu(z) and the RMS norm in
+        groups.  Returns [n, heads * vdim] (T)."""
+        r = i if run is None else run
+        m, w, lib, dev, n = self.spec.layers[i].mixer, self.w, self.lib, self.device, c.n
+        p = f"l{i}."
+        with self.timed("gemm in"):
+            proj = self._linear(h, w[p + "in"])
+        ld, es, base = proj.stride(0), proj.element_size(), proj.data_ptr()
+        stride, st = c.state.storage.stride(0), self._stream()
+        xbc = torch.empty(n, m.conv_channels, dtype=torch.float32, device=dev)
+        with self.timed("short conv + silu"):
+            H.check(lib.b200h_short_conv(base + es * m.inner, ld, w[p + "conv"].data_ptr(), w[p + "conv.b"].data_ptr(), 1,
+                                         c.state.ptr(self.conv_off[r]), stride, c.tok_seq.data_ptr(), c.cu_q.data_ptr(),
+                                         c.seq_slot.data_ptr(), xbc.data_ptr(), n, c.batch, m.conv_channels, m.conv_taps, self.dt, st),
+                    "short_conv")
+        o = torch.empty(n, m.inner, dtype=torch.float32, device=dev)
+        with self.timed("state-space scan"):
+            H.check(lib.b200h_ssm_scan(xbc.data_ptr(), base + es * (m.inner + m.conv_channels), ld, w[p + "dt_bias"].data_ptr(),
+                                       w[p + "A_log"].data_ptr(), w[p + "D"].data_ptr(), c.state.ptr(self.mix_off[r]), stride,
+                                       c.cu_q.data_ptr(), c.seq_slot.data_ptr(), c.batch, m.heads, m.vdim, m.state, m.groups,
+                                       o.data_ptr(), self.dt, st), "ssm_scan")
+        y = torch.empty(n, m.inner, dtype=self.T, device=dev)
+        with self.timed("gate + grouped norm"):
+            H.check(lib.b200h_gate_group_norm(o.data_ptr(), base, ld, w[p + "mixnorm"].data_ptr(), n, m.inner, m.norm_groups,
+                                              self.spec.norm_eps, y.data_ptr(), self.dt, st), "gate_group_norm")
         return y
 
     def dense_mlp(self, i, h):
@@ -530,6 +731,13 @@ class HybridModel:
 
     def _logits(self, xn):
         """Float logits of normed rows: bf16 operands keep a float result (no rounding of the logits to bf16)."""
+        out = self._head_product(xn)
+        cap = self.spec.logit_softcap
+        if cap > 0 and out.numel():
+            H.check(self.lib.b200h_softcap(out.data_ptr(), out.numel(), cap, self._stream()), "softcap")
+        return out
+
+    def _head_product(self, xn):
         head = self.w["head"]
         if self.T is torch.float32 or xn.device.type != "cuda":
             return torch.mm(xn.float(), head.float().t())
@@ -554,7 +762,7 @@ class HybridModel:
         for l in self.spec.layers:
             if l.mixer.kind == "latent_attention":
                 key.append(self.attention_splits(n, l.mixer.heads, max_pos))
-            elif l.mixer.kind == "window_attention":
+            elif l.mixer.kind in ("window_attention", "conv_attention"):
                 key.append((self.window_splits(n, l.mixer.window, max_pos), self.window_score_ld(l.mixer.window, max_pos)))
         return tuple(key)
 
@@ -656,15 +864,18 @@ class HybridModel:
         return y
 
     def routed_experts(self, i, x, xt, n):
-        """Routed experts of layer i: the router reads the float stream x, the experts its T copy xt.  Returns float
-        [n, top, width]: each chosen expert's output times its score (summed by the norm that follows)."""
+        """Routed experts of layer i: the router reads the float stream x (or, when x is None, the experts' own input xt), the
+        experts the T rows xt.  The spec chooses the router's scores (softmax / sigmoid), the expert's activation and whether a
+        score scales the expert's output or its input.  Returns float [n, top, width]: each chosen expert's (weighted) output,
+        summed by the kernel that takes it into the stream."""
         f, w, lib, dev = self.spec.layers[i].mlp, self.w, self.lib, self.device
         p, W, st = f"l{i}.", self.spec.width, self._stream()
         ids = torch.empty(n, f.top, dtype=torch.int32, device=dev)
         wts = torch.empty(n, f.top, dtype=torch.float32, device=dev)
         with self.timed("router"):
-            H.check(lib.b200h_route(x.data_ptr(), w[p + "router"].data_ptr(), n, W, f.experts, f.top, ids.data_ptr(), wts.data_ptr(), st),
-                    "route")
+            src, src_dt = (xt, self.dt) if x is None else (x, H.F32)
+            H.check(lib.b200h_route_scored(src.data_ptr(), src_dt, w[p + "router"].data_ptr(), n, W, f.experts, f.top, H.SCORE_FN[f.score],
+                                           ids.data_ptr(), wts.data_ptr(), st), "route")
         out = torch.empty(n, f.top, W, dtype=torch.float32, device=dev)
         self.last_routing = (ids, wts)
         if n * f.top >= self.grouped_experts_rows * f.experts:
@@ -674,7 +885,10 @@ class HybridModel:
         with self.timed("experts"):
             a = H.ExpertArgs()
             a.n, a.width, a.ff, a.experts, a.top, a.dtype = n, W, f.ff, f.experts, f.top, self.dt
-            a.x, a.gate, a.up, a.down = xt.data_ptr(), w[p + "gate"].data_ptr(), w[p + "up"].data_ptr(), w[p + "down"].data_ptr()
+            a.act, a.scale_input = H.EXPERT_ACT[f.act], int(f.scale_input)
+            a.x, a.up, a.down = xt.data_ptr(), w[p + "up"].data_ptr(), w[p + "down"].data_ptr()
+            if f.act == "silu_gate":
+                a.gate = w[p + "gate"].data_ptr()
             a.ids, a.wts, a.out = ids.data_ptr(), wts.data_ptr(), out.data_ptr()
             mid = torch.empty(n * f.top, f.ff, dtype=self.T, device=dev)
             lists = torch.empty(f.experts * (n * f.top + 1), dtype=torch.int32, device=dev)
@@ -684,7 +898,8 @@ class HybridModel:
 
     def _grouped_experts(self, i, xt, ids, wts, out, n):
         """Prompt portions: rows are sorted by chosen expert (one host read of the per-expert counts), every expert runs its
-        gate / up / down GEMMs over its rows, and the results return to their (row, choice) places times the router's score.
+        gate / up / down GEMMs over its rows, and the results return to their (row, choice) places times the router's score
+        (a score that scales the expert's input goes to the first product's rows instead, inside the activation kernel).
         A step of few rows uses the expert-major kernels instead (b200h_experts: no host read, every expert's weights once)."""
         f, w, lib, st = self.spec.layers[i].mlp, self.w, self.lib, self._stream()
         p = f"l{i}."
@@ -694,18 +909,26 @@ class HybridModel:
         xg = xt.index_select(0, torch.div(order, f.top, rounding_mode="floor"))
         m = n * f.top
         res = torch.empty(m, self.spec.width, dtype=self.T, device=self.device)
+        if f.scale_input and f.act != "relu2":
+            raise NotImplementedError("grouped experts: a score on the input of a gated expert")
+        w_in = wts.view(-1).index_select(0, order).contiguous() if f.scale_input else None
         at = 0
         for e, cnt in enumerate(counts):
             if cnt == 0:
                 continue
             seg = xg[at:at + cnt]
-            g, u = torch.mm(seg, w[p + "gate"][e].t()), torch.mm(seg, w[p + "up"][e].t())
-            H.check(lib.b200h_silu_mul(g.data_ptr(), u.data_ptr(), g.data_ptr(), g.numel(), self.dt, st), "silu_mul")
+            if f.act == "relu2":
+                g = torch.mm(seg, w[p + "up"][e].t())
+                H.check(lib.b200h_scaled_relu2(g.data_ptr(), None if w_in is None else w_in.data_ptr() + 4 * at, cnt, f.ff, self.dt, st),
+                        "scaled_relu2")
+            else:
+                g, u = torch.mm(seg, w[p + "gate"][e].t()), torch.mm(seg, w[p + "up"][e].t())
+                H.check(lib.b200h_silu_mul(g.data_ptr(), u.data_ptr(), g.data_ptr(), g.numel(), self.dt, st), "silu_mul")
             torch.mm(g, w[p + "down"][e].t(), out=res[at:at + cnt])
             at += cnt
         slot = order.to(torch.int32)
-        H.check(lib.b200h_weighted_scatter(res.data_ptr(), slot.data_ptr(), wts.data_ptr(), out.data_ptr(), m, self.spec.width, self.dt, st),
-                "weighted_scatter")
+        H.check(lib.b200h_weighted_scatter(res.data_ptr(), slot.data_ptr(), None if f.scale_input else wts.data_ptr(), out.data_ptr(), m,
+                                           self.spec.width, self.dt, st), "weighted_scatter")
 
     def argmax(self, logits):
         """Greedy ids of float logits [r, vocab] (device int32 [r])."""

@@ -171,10 +171,61 @@ class WindowAttentionSpec:
 
 
 @dataclass(frozen=True)
+class ConvAttentionSpec:
+    """Causal softmax attention with grouped key/value heads whose query and key projections each pass a short causal
+    convolution per channel (taps weights, no bias, the last column is the current token's).  The convolved q and k are rotated
+    (RotarySpec, interleaved pairs of the first rot.dims dimensions of every head) and THEN divided by their root mean square
+    per head (no weight).  values_from_keys: there is no value projection, a key/value head's value is its convolved key before
+    rotation and norm (so vdim == dim).  sink: a constant score that joins the softmax denominator and carries no value
+    (p_j = exp(s_j) / (exp(sink) + sum exp(s_j))); None: a plain softmax."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    conv_taps: int
+    rot: RotarySpec
+    window: int = 0               # visible positions, the query's own included; 0: all earlier positions
+    sink: float = 0.0
+    values_from_keys: bool = True
+    kind = "conv_attention"
+
+
+@dataclass(frozen=True)
+class SsmSpec:
+    """Selective state-space mixer with a scalar decay per head and token.  One projection yields z | x | B | C | dt
+    (inner = heads * vdim, groups * state each for B and C, one dt per head); x, B and C pass a short causal convolution with
+    bias and silu; dt <- softplus(dt + dt_bias); per head S <- exp(-exp(A_log) dt) S + dt B x^T ([state, vdim], float),
+    y = S^T C + D x; y * silu(z) is RMS-normed in norm_groups equal parts, times a weight, then projected."""
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    norm_groups: int
+    conv_taps: int
+    kind = "mamba2"
+
+    @property
+    def inner(self):
+        return self.heads * self.vdim
+
+    @property
+    def conv_channels(self):
+        return self.inner + 2 * self.groups * self.state
+
+    @property
+    def proj_cols(self):
+        return 2 * self.inner + 2 * self.groups * self.state + self.heads
+
+
+@dataclass(frozen=True)
 class RoutedExpertsSpec:
     experts: int
     top: int
     ff: int
+    score: str = "softmax"        # router scores: 'softmax' over all experts | 'sigmoid' of every logit on its own
+    act: str = "silu_gate"        # expert: 'silu_gate' = down(silu(gate h) * up h) | 'relu2' = down(relu(up h)^2), no gate matrix
+    scale_input: bool = False     # the router's score multiplies the expert's input instead of its output
     kind = "moe"
 
 
@@ -188,7 +239,7 @@ class DenseMlpSpec:
 
 @dataclass(frozen=True)
 class HybridLayerSpec:
-    mixer: object                       # LatentAttentionSpec | DecayAttentionSpec | WindowAttentionSpec
+    mixer: object                       # LatentAttentionSpec | DecayAttentionSpec | WindowAttentionSpec | ConvAttentionSpec | SsmSpec
     mlp: object = None                  # RoutedExpertsSpec | DenseMlpSpec | None: the layer has no feed-forward
 
 
@@ -212,6 +263,12 @@ class HybridSpec:
     max_positions: int = 0              # > 0: a learned vector per position is added to the embedding
     loop: tuple = None                  # (start, stop, times): layers start..stop-1 run `times` times in a row with the same weights,
     #                                     each pass with a cache and state of its own and a learned vector added before it
+    # 'parallel' blocks: both sublayers read the SAME stream through offset norms of their own and their outputs join it together,
+    #              x <- x + residual_mult * (mixer(n1(x)) + ff(n2(x))); the mixers carry their own convolutions (conv_taps is unused).
+    residual_mult: float = 1.0
+    logit_softcap: float = 0.0          # > 0: logits <- cap * tanh(logits / cap)
+    tied_head: bool = False             # the head is the embedding table (no 'head' tensor)
+    loop_readds_embedding: bool = False  # every pass of the loop but the first adds the embedding output to the stream before its vector
     hybrid = True
 
     @property
@@ -279,18 +336,62 @@ def bodopel_spec(cfg, name="bodopel"):
                 raise NotImplementedError(f"feed-forward kind {mlp.get('kind')!r}")
             mlp = DenseMlpSpec(int(mlp["ff"]))
         layers.append(HybridLayerSpec(mixer, mlp))
-    loop = cfg.get("loop")
-    if loop is not None:
-        loop = (int(loop["start"]), int(loop["stop"]), int(loop["times"]))
-        if not 0 <= loop[0] <= loop[1] <= len(layers) or loop[2] < 1:
-            raise ValueError(f"loop {loop} over {len(layers)} layers")
-        if loop[0] == loop[1]:
-            loop = None
+    loop = _loop_of(cfg, len(layers))
     return HybridSpec(name=name, arch="bodopel", width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=tuple(layers),
                       norm_eps=float(cfg["norm"]["eps"]), norm_groups=1, conv_taps=int(cfg["canon"]["taps"]),
                       embedding_scale=float(cfg["embedding"]["scale"]), session_len=int(cfg["max_positions"]), block="pre_norm",
                       max_positions=int(cfg["max_positions"]), loop=loop)
 
 
+def _loop_of(cfg, layers):
+    loop = cfg.get("loop")
+    if loop is None:
+        return None
+    loop = (int(loop["start"]), int(loop["stop"]), int(loop["times"]))
+    if not 0 <= loop[0] <= loop[1] <= layers or loop[2] < 1:
+        raise ValueError(f"loop {loop} over {layers} layers")
+    return None if loop[0] == loop[1] else loop
+
+
+def _lifuzen_mixer(kind, m):
+    if kind == "attention":
+        heads, kv_heads, dim = int(m["heads"]), int(m["kv_heads"]), int(m["dim"])
+        vdim = int(m.get("vdim", dim))
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads do not divide into {kv_heads} key/value heads")
+        if vdim != dim:
+            raise ValueError(f"vdim {vdim} != dim {dim}: the values of this attention are its keys")
+        rot = RotarySpec(int(m["rot"]["dims"]), float(m["rot"]["base"]))
+        if rot.dims > dim or rot.dims % 2 or dim % 2:
+            raise ValueError(f"rot.dims {rot.dims} does not fit dim {dim} (both even)")
+        return ConvAttentionSpec(heads, kv_heads, dim, vdim, float(m["scale"]), int(m["conv"]), rot)
+    if kind == "mamba2":
+        s = SsmSpec(int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"]), int(m["norm_groups"]), int(m["conv"]))
+        if s.heads % s.groups or s.inner % s.norm_groups:
+            raise ValueError(f"{s.heads} heads in {s.groups} groups, {s.inner} channels in {s.norm_groups} norm groups")
+        return s
+    raise NotImplementedError(f"mixer type {kind!r}")
+
+
+def lifuzen_spec(cfg, name="lifuzen"):
+    """config.json of a Lifuzen checkpoint -> HybridSpec.  Every size and constant is read from the config."""
+    layers = []
+    for entry in cfg["layers"]:
+        mlp = entry.get("mlp")
+        if mlp is not None:
+            if mlp.get("kind", "moe") != "moe":
+                raise NotImplementedError(f"feed-forward kind {mlp.get('kind')!r}")
+            mlp = RoutedExpertsSpec(int(mlp["router"]["experts"]), int(mlp["router"]["top"]), int(mlp["expert"]["ff"]),
+                                    score="sigmoid", act="relu2", scale_input=True)
+            if not 1 <= mlp.top <= mlp.experts:
+                raise ValueError(f"top {mlp.top} of {mlp.experts} experts")
+        layers.append(HybridLayerSpec(_lifuzen_mixer(entry["type"], entry["mixer"]), mlp))
+    return HybridSpec(name=name, arch="lifuzen", width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=tuple(layers),
+                      norm_eps=float(cfg["norm"]["eps"]), norm_groups=1, conv_taps=1, embedding_scale=1.0,
+                      session_len=int(cfg.get("session_len", 0)), block="parallel", loop=_loop_of(cfg, len(layers)),
+                      residual_mult=float(cfg.get("residual_mult", 1.0)), logit_softcap=float(cfg.get("logit_softcap") or 0.0),
+                      tied_head=True, loop_readds_embedding=True)
+
+
 # config.json "architecture" -> spec builder, for checkpoints that are not HF `architectures` configs
-HYBRID_ARCHITECTURES = {"Gulozen": gulozen_spec, "Bodopel": bodopel_spec}
+HYBRID_ARCHITECTURES = {"Gulozen": gulozen_spec, "Bodopel": bodopel_spec, "Lifuzen": lifuzen_spec}

@@ -176,9 +176,16 @@ class EmulatedHybridLib:
         return 0
 
     def b200h_route(self, x, router, n, width, experts, top, ids, wts, stream):
+        return self.b200h_route_scored(x, F32, router, n, width, experts, top, 0, ids, wts, stream)
+
+    def b200h_route_scored(self, x, x_dtype, router, n, width, experts, top, score_fn, ids, wts, stream):
+        assert x_dtype == F32
         z = _f(x, n, width) @ _f(router, experts, width).T
-        e = np.exp(z - z.max(-1, keepdims=True))
-        sc = e / e.sum(-1, keepdims=True)
+        if score_fn == 1:
+            sc = _sigmoid(z)
+        else:
+            e = np.exp(z - z.max(-1, keepdims=True))
+            sc = e / e.sum(-1, keepdims=True)
         order = np.argsort(-sc, -1, kind="stable")[:, :top]
         _i(ids, n * top).reshape(n, top)[:] = order
         _f(wts, n, top)[:] = np.take_along_axis(sc, order, -1)
@@ -188,13 +195,19 @@ class EmulatedHybridLib:
         a = args._obj
         n, top, width, ff, E = a.n, a.top, a.width, a.ff, a.experts
         X, idx, wt = _f(a.x, n, width), _i(a.ids, n * top).reshape(n, top), _f(a.wts, n, top)
-        G, U, Dn = _f(a.gate, E, ff, width), _f(a.up, E, ff, width), _f(a.down, E, width, ff)
+        U, Dn = _f(a.up, E, ff, width), _f(a.down, E, width, ff)
+        G = _f(a.gate, E, ff, width) if a.act == 0 else None
         O = _f(a.out, n, top, width)
         for t in range(n):
             for k in range(top):
                 e = idx[t, k]
-                g = G[e] @ X[t]
-                O[t, k] = wt[t, k] * (Dn[e] @ (g * _sigmoid(g) * (U[e] @ X[t])))
+                xin = X[t] * wt[t, k] if a.scale_input else X[t]
+                if a.act == 0:
+                    g = G[e] @ xin
+                    mid = g * _sigmoid(g) * (U[e] @ xin)
+                else:
+                    mid = np.maximum(U[e] @ xin, 0) ** 2
+                O[t, k] = (Dn[e] @ mid) * (np.float32(1) if a.scale_input else wt[t, k])
         return 0
 
     def b200h_silu_mul(self, g, u, out, count, dtype, stream):
@@ -203,7 +216,8 @@ class EmulatedHybridLib:
         return 0
 
     def b200h_weighted_scatter(self, src, slot, wts, out, rows, width, dtype, stream):
-        S_, to, wt = _f(src, rows, width), _i(slot, rows), _a(wts, rows)
+        S_, to = _f(src, rows, width), _i(slot, rows)
+        wt = _a(wts, rows) if wts else np.ones(rows, np.float32)
         _f(out, rows, width)[to] = wt[to][:, None] * S_
         return 0
 
@@ -279,12 +293,117 @@ class EmulatedHybridLib:
                     sc = a.softcap * np.tanh(sc / a.softcap)
                 if a.r1:
                     sc = sc - _f(a.r1, H)[h] * np.log1p(_f(a.r2, H)[h] * dist)
-                e = np.exp(sc - sc.max())
-                wts[h] = e / e.sum()
+                if a.sink:
+                    mx = max(float(sc.max()), float(_f(a.sink, H)[h]))
+                    e = np.exp(sc - mx)
+                    wts[h] = e / (e.sum() + np.exp(_f(a.sink, H)[h] - mx))
+                else:
+                    e = np.exp(sc - sc.max())
+                    wts[h] = e / e.sum()
             if a.talk:
                 wts = _f(a.talk, H, H) @ wts
             out = np.stack([wts[h] @ vs[:, h // rep] for h in range(H)]).reshape(H * V)
             y[t] = out * _sigmoid(gate[t]) if gate is not None else out
+        return 0
+
+    # ---- parallel blocks, convolved rotary attention, state-space mixer
+    def b200h_parallel_residual_norm(self, x, mix, ff, parts, mult, add, extra, w1, w2, n, width, eps, h1, h2, dtype, stream):
+        X = _f(x, n, width)
+        if mix or ff:
+            y = _f(mix, n, width).copy() if mix else np.zeros((n, width), np.float32)
+            if ff:
+                y += _f(ff, n, parts, width).sum(1)
+            X += np.float32(mult) * y
+        if add:
+            X += _f(add, n, width)
+        if extra:
+            X += _f(extra, width)
+        for h, w in ((h1, w1), (h2, w2)):
+            if h:
+                _f(h, n, width)[:] = _unit(X, eps) * _f(w, width)
+        return 0
+
+    @staticmethod
+    def _conv_rows(U, Wt, bias, state, slot_stride, cu, slots, batch, taps):
+        """Causal taps over every entry's rows with its state in front; advances the state.  -> [n, channels]."""
+        n, ch = U.shape
+        out = np.zeros((n, ch), np.float32)
+        for s in range(batch):
+            lo, hi = cu[s], cu[s + 1]
+            if lo == hi:
+                continue
+            st = _f(int(state) + 4 * int(slots[s]) * slot_stride, taps - 1, ch)
+            full = np.concatenate([st, U[lo:hi]], 0)
+            for t in range(hi - lo):
+                acc = np.zeros(ch, np.float32) if bias is None else bias.copy()
+                for j in range(taps):
+                    acc += Wt[:, j] * full[t + j]
+                out[lo + t] = acc
+            st[:] = full[full.shape[0] - (taps - 1):]
+        return out
+
+    def b200h_short_conv(self, u, ld, w, bias, act, state, slot_stride, tok_seq, cu_q, seq_slot, out, n, batch, channels, taps, dtype, stream):
+        assert dtype == F32
+        y = self._conv_rows(_rows(u, n, ld, channels), _f(w, channels, taps), _f(bias, channels) if bias else None, state, slot_stride,
+                            _i(cu_q, batch + 1), _i(seq_slot, batch), batch, taps)
+        _f(out, n, channels)[:] = y * _sigmoid(y) if act == 1 else y
+        return 0
+
+    def b200h_ssm_scan(self, xbc, dt, ld_dt, dt_bias, a_log, skip, state, slot_stride, cu_q, seq_slot, batch, heads, vdim, nstate, groups,
+                       out, dtype, stream):
+        cu, slots = _i(cu_q, batch + 1), _i(seq_slot, batch)
+        n, inner, gn = int(cu[batch]), heads * vdim, groups * nstate
+        X = _f(xbc, n, inner + 2 * gn)
+        DT = _rows(dt, n, ld_dt, heads) + _f(dt_bias, heads)
+        DT = (np.maximum(DT, 0) + np.log1p(np.exp(-np.abs(DT)))).astype(np.float32)
+        rate, D, O = np.exp(_f(a_log, heads)), _f(skip, heads), _f(out, n, heads, vdim)
+        for s in range(batch):
+            S = _f(int(state) + 4 * int(slots[s]) * slot_stride, heads, vdim, nstate)
+            for t in range(cu[s], cu[s + 1]):
+                for h in range(heads):
+                    g = h // (heads // groups)
+                    xv = X[t, h * vdim:(h + 1) * vdim]
+                    B, Cm = X[t, inner + g * nstate:inner + (g + 1) * nstate], X[t, inner + gn + g * nstate:inner + gn + (g + 1) * nstate]
+                    S[h] = np.exp(-rate[h] * DT[t, h]) * S[h] + DT[t, h] * np.outer(xv, B)
+                    O[t, h] = S[h] @ Cm + D[h] * xv
+        return 0
+
+    def b200h_gate_group_norm(self, y, gate, ld_gate, w, n, count, groups, eps, out, dtype, stream):
+        z = _rows(gate, n, ld_gate, count)
+        v = _f(y, n, count) * (z * _sigmoid(z))
+        _f(out, n, count)[:] = _unit(v.reshape(n, groups, count // groups), eps).reshape(n, count) * _f(w, count)
+        return 0
+
+    def b200h_conv_rope_prep(self, args):
+        a = args._obj
+        assert a.dtype == F32
+        H, G, D = a.heads, a.kv_heads, a.dim
+        ch = (H + G) * D
+        y = self._conv_rows(_rows(a.qk, a.n, a.ld, ch), _f(a.conv, ch, a.taps), None, a.state, a.slot_stride, _i(a.cu_q, a.batch + 1),
+                            _i(a.seq_slot, a.batch), a.batch, a.taps)
+        seqs, poss = _i(a.tok_seq, a.n), _i(a.tok_pos, a.n)
+        qn = _f(a.qn, a.n, H, D)
+
+        class _Geo:          # what _kv reads
+            cu_blocks, block_ptrs, block_len, layer_off, v_off, kv_heads, dim, vdim = a.cu_blocks, a.block_ptrs, a.block_len, a.layer_off, a.v_off, G, D, D
+        for t in range(a.n):
+            heads = y[t].reshape(H + G, D)
+            kd, vd = self._kv(_Geo, int(seqs[t]), int(poss[t]))
+            vd[:] = heads[H:]
+            turned = _unit(self._rot(heads, int(poss[t]), a), a.eps)
+            qn[t] = turned[:H]
+            kd[:] = turned[H:]
+        return 0
+
+    def b200h_softcap(self, x, count, cap, stream):
+        X = _a(x, count)
+        X[:] = np.float32(cap) * np.tanh(X / np.float32(cap))
+        return 0
+
+    def b200h_scaled_relu2(self, u, scale, rows, cols, dtype, stream):
+        U = _f(u, rows, cols)
+        sc = _a(scale, rows)[:, None] if scale else np.float32(1)
+        U[:] = np.maximum(U * sc, 0) ** 2
         return 0
 
     def b200h_argmax(self, logits, ld, rows, vocab, out, stream):
