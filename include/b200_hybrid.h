@@ -207,10 +207,10 @@ B200H_API int b200h_window_attention(const b200h_window_args* args);
 
 /* x[t] += mult * (mix[t] + sum_p ff[t, p]) + add[t] + extra, then h1[t] = x[t] / rms(x[t]) * w1 and h2[t] = ... * w2 as T.
  * mix T [n, width], ff float [n, parts, width], add float [n, width], extra T [width], h1, h2: each optional (NULL);
- * w1 / w2 float [width] hold the full factor. */
+ * w1 / w2 float [width] hold the full factor; h2f (optional, with h2): the second norm as float too. */
 B200H_API int b200h_parallel_residual_norm(void* x, const void* mix, const void* ff, int parts, float mult, const void* add, const void* extra,
-                                           const void* w1, const void* w2, int n, int width, float eps, void* h1, void* h2, int dtype,
-                                           void* stream);
+                                           const void* w1, const void* w2, int n, int width, float eps, void* h1, void* h2, void* h2f,
+                                           int dtype, void* stream);
 
 /* out[t, c] = act(bias[c] + sum_j w[c, j] * u[t - taps + 1 + j, c]) as float [n, channels]; u T with row stride ld; w float
  * [channels, taps]; bias float [channels] or NULL; act 0 none, 1 silu.  Rows before an entry's first come from its state (float

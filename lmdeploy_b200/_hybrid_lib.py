@@ -104,7 +104,7 @@ def load():
     lib.b200h_window_prep.argtypes = [C.POINTER(WindowArgs)]
     lib.b200h_window_attention.argtypes = [C.POINTER(WindowArgs)]
     lib.b200h_route_scored.argtypes = [P, I, P, I, I, I, I, I, P, P, P]
-    lib.b200h_parallel_residual_norm.argtypes = [P, P, P, I, F, P, P, P, P, I, I, F, P, P, I, P]
+    lib.b200h_parallel_residual_norm.argtypes = [P, P, P, I, F, P, P, P, P, I, I, F, P, P, P, I, P]
     lib.b200h_short_conv.argtypes = [P, L64, P, P, I, P, L64, P, P, P, P, I, I, I, I, I, P]
     lib.b200h_ssm_scan.argtypes = [P, P, L64, P, P, P, P, L64, P, P, I, I, I, I, I, P, I, P]
     lib.b200h_gate_group_norm.argtypes = [P, P, L64, P, I, I, I, F, P, I, P]

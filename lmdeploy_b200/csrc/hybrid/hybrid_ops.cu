@@ -481,7 +481,18 @@ __global__ void route_kernel(const TI* __restrict__ x, const float* __restrict__
     if (threadIdx.x == 0) {
         float inv = 1.0f;
         if (score_fn == 1) {
-            for (int e = 0; e < experts; ++e) z[e] = sigmoid_f(z[e]);
+            // the sigmoid is monotonic: the choice is made on the logits themselves (two large logits whose sigmoids both round
+            // to one are still told apart), and only the chosen ones' sigmoids are taken
+            for (int k = 0; k < top; ++k) {
+                int best = -1;
+                float bv = -INFINITY;
+                for (int e = 0; e < experts; ++e)
+                    if (z[e] > bv || best < 0) { bv = z[e]; best = e; }
+                ids[(size_t)t * top + k] = best;
+                wts[(size_t)t * top + k] = sigmoid_f(bv);
+                z[best] = -INFINITY;
+            }
+            return;
         } else {
             float mx = z[0];
             for (int e = 1; e < experts; ++e) mx = fmaxf(mx, z[e]);
@@ -1147,16 +1158,16 @@ B200H_API int b200h_window_attention(const b200h_window_args* a)
 
 // ------------------------------------------------------------------------------------------------ parallel blocks, state-space mixer
 B200H_API int b200h_parallel_residual_norm(void* x, const void* mix, const void* ff, int parts, float mult, const void* add, const void* extra,
-                                           const void* w1, const void* w2, int n, int width, float eps, void* h1, void* h2, int dtype,
-                                           void* stream)
+                                           const void* w1, const void* w2, int n, int width, float eps, void* h1, void* h2, void* h2f,
+                                           int dtype, void* stream)
 {
-    if (!x || n < 0 || width <= 0 || (h1 && !w1) || (h2 && !w2) || (ff && parts < 1))
+    if (!x || n < 0 || width <= 0 || (h1 && !w1) || ((h2 || h2f) && !w2) || (h2f && !h2) || (ff && parts < 1))
         return fail(B200H_ERR_INVALID_ARG, "parallel_residual_norm: bad arguments");
     if (n == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     B200H_DISPATCH_T(dtype, parallel_residual_norm_kernel<T><<<n, 256, 0, st>>>((float*)x, (const T*)mix, (const float*)ff, ff ? parts : 0, mult,
                                                                                (const float*)add, (const T*)extra, (const float*)w1,
-                                                                               (const float*)w2, width, eps, (T*)h1, (T*)h2));
+                                                                               (const float*)w2, width, eps, (T*)h1, (T*)h2, (float*)h2f));
     return launched("parallel_residual_norm");
 }
 

@@ -5,12 +5,13 @@
 
 // x[t] += mult * (mix[t] + sum_p ff[t, p]) + add[t] + extra;  h1[t] = x[t] / rms(x[t]) * w1,  h2[t] = x[t] / rms(x[t]) * w2  (as T).
 // mix (T [n, width]), ff (float [n, parts, width]), add (float [n, width]), extra (T [width]), h1 and h2 are optional; the two norms
-// share one root mean square.  w1 / w2 hold the full factor (one plus the stored deviation).
+// share one root mean square.  w1 / w2 hold the full factor (one plus the stored deviation).  h2f (optional): the second norm's
+// result as float as well, for a router that reads it unrounded.
 template <typename T>
 __global__ void parallel_residual_norm_kernel(float* __restrict__ x, const T* __restrict__ mix, const float* __restrict__ ff, int parts,
                                               float mult, const float* __restrict__ add, const T* __restrict__ extra,
                                               const float* __restrict__ w1, const float* __restrict__ w2, int width, float eps,
-                                              T* __restrict__ h1, T* __restrict__ h2)
+                                              T* __restrict__ h1, T* __restrict__ h2, float* __restrict__ h2f)
 {
     __shared__ float red[32];
     const size_t base = (size_t)blockIdx.x * width;
@@ -34,6 +35,7 @@ __global__ void parallel_residual_norm_kernel(float* __restrict__ x, const T* __
         const float v = x[base + i] * r;               // written above by this same thread
         if (h1) h1[base + i] = from_f<T>(v * w1[i]);
         if (h2) h2[base + i] = from_f<T>(v * w2[i]);
+        if (h2f) h2f[base + i] = v * w2[i];
     }
 }
 

@@ -507,6 +507,7 @@ class HybridModel:
             e0 = x.clone() if s.loop is not None and s.loop_readds_embedding and s.loop[2] > 1 else None
         h1 = torch.empty(n, W, dtype=T, device=dev)
         h2 = torch.empty(n, W, dtype=T, device=dev)
+        h2f = torch.empty(n, W, dtype=torch.float32, device=dev)         # the router reads the second norm unrounded
         mix = ff = None                  # the previous run's outputs that the stream has not taken in yet
         parts = 0
 
@@ -515,7 +516,8 @@ class HybridModel:
                 H.check(lib.b200h_parallel_residual_norm(
                     x.data_ptr(), None if mix is None else mix.data_ptr(), None if ff is None else ff.data_ptr(), parts, s.residual_mult,
                     add, extra, None if w1 is None else w1.data_ptr(), None if w2 is None else w2.data_ptr(), n, W, eps,
-                    None if w1 is None else h1.data_ptr(), None if w2 is None else h2.data_ptr(), dt, st), "parallel_residual_norm")
+                    None if w1 is None else h1.data_ptr(), None if w2 is None else h2.data_ptr(), None if w2 is None else h2f.data_ptr(),
+                    dt, st), "parallel_residual_norm")
 
         for r, (i, t) in enumerate(self.runs):
             p, layer = f"l{i}.", s.layers[i]
@@ -533,7 +535,7 @@ class HybridModel:
             if f is not None:
                 if f.kind != "moe":
                     raise NotImplementedError(f"parallel blocks with a {f.kind!r} feed-forward")
-                ff, parts = self.routed_experts(i, None, h2, n), f.top
+                ff, parts = self.routed_experts(i, h2f, h2, n), f.top
             if trace is not None:
                 join(None, None, None, None)
                 mix = ff = None
@@ -878,7 +880,8 @@ class HybridModel:
                                            ids.data_ptr(), wts.data_ptr(), st), "route")
         out = torch.empty(n, f.top, W, dtype=torch.float32, device=dev)
         self.last_routing = (ids, wts)
-        if n * f.top >= self.grouped_experts_rows * f.experts:
+        capturing = dev.type == "cuda" and torch.cuda.is_current_stream_capturing()      # the grouped path reads counts on the host
+        if n * f.top >= self.grouped_experts_rows * f.experts and not capturing:
             with self.timed("experts (grouped GEMMs)"):
                 self._grouped_experts(i, xt, ids, wts, out, n)
             return out

@@ -96,6 +96,8 @@ class EmulatedHybridLib:
 
     @staticmethod
     def _rot(v, pos, a):
+        if a.rot.pairs == 0:
+            return v.copy()
         f = _a(a.rot.freqs, a.rot.pairs, C.c_double)
         ang = float(pos) * f
         c, s = (np.cos(ang) * a.rot.magnitude).astype(np.float32), (np.sin(ang) * a.rot.magnitude).astype(np.float32)
@@ -182,7 +184,10 @@ class EmulatedHybridLib:
         assert x_dtype == F32
         z = _f(x, n, width) @ _f(router, experts, width).T
         if score_fn == 1:
-            sc = _sigmoid(z)
+            order = np.argsort(-z, -1, kind="stable")[:, :top]          # chosen on the logits: the sigmoid keeps their order
+            _i(ids, n * top).reshape(n, top)[:] = order
+            _f(wts, n, top)[:] = _sigmoid(np.take_along_axis(z, order, -1))
+            return 0
         else:
             e = np.exp(z - z.max(-1, keepdims=True))
             sc = e / e.sum(-1, keepdims=True)
@@ -307,7 +312,7 @@ class EmulatedHybridLib:
         return 0
 
     # ---- parallel blocks, convolved rotary attention, state-space mixer
-    def b200h_parallel_residual_norm(self, x, mix, ff, parts, mult, add, extra, w1, w2, n, width, eps, h1, h2, dtype, stream):
+    def b200h_parallel_residual_norm(self, x, mix, ff, parts, mult, add, extra, w1, w2, n, width, eps, h1, h2, h2f, dtype, stream):
         X = _f(x, n, width)
         if mix or ff:
             y = _f(mix, n, width).copy() if mix else np.zeros((n, width), np.float32)
@@ -318,7 +323,7 @@ class EmulatedHybridLib:
             X += _f(add, n, width)
         if extra:
             X += _f(extra, width)
-        for h, w in ((h1, w1), (h2, w2)):
+        for h, w in ((h1, w1), (h2, w2), (h2f, w2)):
             if h:
                 _f(h, n, width)[:] = _unit(X, eps) * _f(w, width)
         return 0
