@@ -78,6 +78,46 @@ def bodopel_bench_config(z, window=1024):
             "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": d["inter"] * 3 // 2}} for _ in HYBRID_LAYERS]}
 
 
+def lifuzen_bench_config(z):
+    """A Lifuzen config.json (dict) of size `z`: the layer pattern of the Gulozen bench (three attention layers and one recurrent
+    layer) with the dense decoder's head geometry for the attention (GQA, 128 dimensions per head of which 64 turn, 4 taps), a
+    state-space mixer of twice the width in heads of 64 channels with a state of 128, and eight squared-relu experts of which two
+    are chosen, with the Gulozen experts' parameter count (two matrices of 1.5 * ff instead of three of ff)."""
+    d = z["dense"]
+    att = {"heads": d["heads"], "kv_heads": d["kv_heads"], "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5,
+           "rot": {"dims": 64, "base": 10000.0}}
+    ssm = {"heads": 2 * z["width"] // 64, "vdim": 64, "state": 128, "groups": 8, "norm_groups": 8, "conv": 4}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"] * 3 // 2}, "router": {"experts": z["experts"], "top": z["top"]}}
+    return {"architecture": "Lifuzen", "norm": {"eps": 1e-6}, "vocab": HYBRID_VOCAB, "width": z["width"], "residual_mult": 0.5,
+            "logit_softcap": 30.0,
+            "layers": [{"type": "attention" if t == "latent_attention" else "mamba2", "mixer": att if t == "latent_attention" else ssm,
+                        "mlp": mlp} for t in HYBRID_LAYERS]}
+
+
+def _hybrid_leg(torch, spec, batch, ctx, steps, warm, session, blocks):
+    """One hybrid decoder through its engine: throughput, then per-operator device time (eight more decode steps, then one fresh
+    4096-row prefill step, bracketed by CUDA events)."""
+    from lmdeploy_b200.messages import TurbomindEngineConfig
+    from lmdeploy_b200.turbomind.engine import TurboMind
+    eng = TurboMind(spec, TurbomindEngineConfig(dtype="bfloat16", max_batch_size=batch, session_len=session, cache_max_entry_count=blocks,
+                                                max_prefill_token_num=8192), seed=0)
+    res, seqs = _engine_throughput(torch, eng, HYBRID_VOCAB, batch, ctx, steps, warm)
+    res["weight_bytes"] = eng.model.weight_bytes
+    eng.model.events = []
+    for _ in range(8):
+        eng.step()
+    res["decode_operator_ms_per_step"] = {k: round(v / 8, 4) for k, v in eng.model.operator_ms().items()}
+    for s in seqs:
+        eng.scheduler.finish(s.session_id)
+    _engine_prefill_once(torch, eng, HYBRID_VOCAB, 4, 1024)
+    eng.model.operator_ms()
+    _engine_prefill_once(torch, eng, HYBRID_VOCAB, 4, 1024)
+    res["prefill_4x1024_operator_ms"] = {k: round(v, 4) for k, v in eng.model.operator_ms().items()}
+    del eng
+    torch.cuda.empty_cache()
+    return res
+
+
 def _engine_throughput(torch, eng, vocab, batch, ctx, steps, warm):
     """Prompts of `ctx` tokens for `batch` requests through TurboMind.step: tokens/s of prompt ingestion (until every request
     has produced its first token) and of `steps` decode steps after `warm` untimed ones.  Wall clock around synchronised
@@ -118,7 +158,7 @@ def run_hybrid(args):
     from lmdeploy_b200.messages import TurbomindEngineConfig
     from lmdeploy_b200.turbomind import ModelSpec
     from lmdeploy_b200.turbomind.engine import TurboMind
-    from lmdeploy_b200.turbomind.specs import bodopel_spec, gulozen_spec
+    from lmdeploy_b200.turbomind.specs import bodopel_spec, gulozen_spec, lifuzen_spec
     z = HYBRID_SIZES[args.hybrid]
     batch, ctx, steps, warm = args.hybrid_batch, args.hybrid_ctx, args.steps, max(args.warmup, 3)
     session = 2 * ctx + warm + steps + 16
@@ -129,25 +169,15 @@ def run_hybrid(args):
         clocks.wait_ready()
         if args.hybrid_design == "bodopel":
             spec = bodopel_spec(bodopel_bench_config(z), name=f"bodopel-{args.hybrid}")
+        elif args.hybrid_design == "lifuzen":
+            spec = lifuzen_spec(lifuzen_bench_config(z), name=f"lifuzen-{args.hybrid}")
         else:
             spec = gulozen_spec(hybrid_config(z), name=f"gulozen-{args.hybrid}")
-        eng = TurboMind(spec, TurbomindEngineConfig(dtype="bfloat16", max_batch_size=batch, session_len=session, cache_max_entry_count=blocks,
-                                                    max_prefill_token_num=8192), seed=0)
-        out["hybrid"], seqs = _engine_throughput(torch, eng, HYBRID_VOCAB, batch, ctx, steps, warm)
-        out["hybrid"]["weight_bytes"] = eng.model.weight_bytes
-        # per-operator device time: eight more decode steps, then one fresh 4096-row prefill step, bracketed by CUDA events
-        eng.model.events = []
-        for _ in range(8):
-            eng.step()
-        out["hybrid"]["decode_operator_ms_per_step"] = {k: round(v / 8, 4) for k, v in eng.model.operator_ms().items()}
-        for s in seqs:
-            eng.scheduler.finish(s.session_id)
-        _engine_prefill_once(torch, eng, HYBRID_VOCAB, 4, 1024)
-        eng.model.operator_ms()
-        _engine_prefill_once(torch, eng, HYBRID_VOCAB, 4, 1024)
-        out["hybrid"]["prefill_4x1024_operator_ms"] = {k: round(v, 4) for k, v in eng.model.operator_ms().items()}
-        del eng
-        torch.cuda.empty_cache()
+        out["hybrid"] = _hybrid_leg(torch, spec, batch, ctx, steps, warm, session, blocks)
+        if args.hybrid_design == "lifuzen":
+            # the closest existing model -- attention with a sink, a recurrent layer, routed experts -- at equal size, same workload
+            out["closest"] = dict(_hybrid_leg(torch, gulozen_spec(hybrid_config(z), name=f"gulozen-{args.hybrid}"), batch, ctx, steps, warm,
+                                              session, blocks), design="gulozen")
         d = z["dense"]
         dspec = ModelSpec(f"dense-{args.hybrid}", "llama", d["hidden"], len(HYBRID_LAYERS), d["heads"], d["kv_heads"], d["inter"], HYBRID_VOCAB,
                           1e4, weight_format="fp16")
@@ -182,9 +212,11 @@ def parse():
     ap.add_argument("--hybrid", default=None, choices=list(HYBRID_SIZES),
                     help="instead of the default workload: prefill and decode tokens/s of a hybrid decoder of this size (--hybrid-design) "
                          "beside the dense decoder of equal size, both through the engine (random weights)")
-    ap.add_argument("--hybrid-design", default="gulozen", choices=["gulozen", "bodopel"],
-                    help="which hybrid design --hybrid builds: Gulozen (latent / decayed linear attention, routed experts) or Bodopel "
-                         "(windowed attention with grouped key/value heads, dense feed-forward)")
+    ap.add_argument("--hybrid-design", default="gulozen", choices=["gulozen", "bodopel", "lifuzen"],
+                    help="which hybrid design --hybrid builds: Gulozen (latent / decayed linear attention, routed experts), Bodopel "
+                         "(windowed attention with grouped key/value heads, dense feed-forward) or Lifuzen (parallel blocks: convolved rotary "
+                         "attention with a sink / state-space mixer, sigmoid-routed squared-relu experts; also runs Gulozen of equal size, the "
+                         "closest existing model, beside it)")
     ap.add_argument("--hybrid-batch", type=int, default=32)
     ap.add_argument("--hybrid-ctx", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true", help="do not capture the step in a CUDA graph")
