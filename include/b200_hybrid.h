@@ -221,10 +221,11 @@ B200H_API int b200h_short_conv(const void* u, int64_t ld, const void* w, const v
 
 /* Per head h (group h / (heads / groups)): dt = softplus(dt + dt_bias[h]); S <- exp(-exp(a_log[h]) dt) S + dt B x^T;
  * out = S^T C + skip[h] x (float [n, heads * vdim]).  xbc float [n, heads * vdim + 2 * groups * nstate] = x | B | C;
- * dt T with row stride ld_dt, one column per head; state float [heads, vdim, nstate] at state + seq_slot[s] * slot_stride. */
+ * dt T with row stride ld_dt, one column per head; state float [heads, vdim, nstate] at state + seq_slot[s] * slot_stride;
+ * steps: float [n, heads, 2] scratch (every row's step size and decay, computed once per head). */
 B200H_API int b200h_ssm_scan(const void* xbc, const void* dt, int64_t ld_dt, const void* dt_bias, const void* a_log, const void* skip,
-                             void* state, int64_t slot_stride, const void* cu_q, const void* seq_slot, int batch, int heads, int vdim,
-                             int nstate, int groups, void* out, int dtype, void* stream);
+                             void* state, int64_t slot_stride, const void* cu_q, const void* seq_slot, int n, int batch, int heads, int vdim,
+                             int nstate, int groups, void* steps, void* out, int dtype, void* stream);
 
 /* out[t] = unit_rms_per_group(y[t] * silu(gate[t])) * w as T; y float [n, count], gate T with row stride ld_gate, `groups` equal parts. */
 B200H_API int b200h_gate_group_norm(const void* y, const void* gate, int64_t ld_gate, const void* w, int n, int count, int groups, float eps,

@@ -106,7 +106,7 @@ def load():
     lib.b200h_route_scored.argtypes = [P, I, P, I, I, I, I, I, P, P, P]
     lib.b200h_parallel_residual_norm.argtypes = [P, P, P, I, F, P, P, P, P, I, I, F, P, P, P, I, P]
     lib.b200h_short_conv.argtypes = [P, L64, P, P, I, P, L64, P, P, P, P, I, I, I, I, I, P]
-    lib.b200h_ssm_scan.argtypes = [P, P, L64, P, P, P, P, L64, P, P, I, I, I, I, I, P, I, P]
+    lib.b200h_ssm_scan.argtypes = [P, P, L64, P, P, P, P, L64, P, P, I, I, I, I, I, I, P, P, I, P]
     lib.b200h_gate_group_norm.argtypes = [P, P, L64, P, I, I, I, F, P, I, P]
     lib.b200h_conv_rope_prep.argtypes = [C.POINTER(ConvPrepArgs)]
     lib.b200h_softcap.argtypes = [P, L64, F, P]

@@ -593,19 +593,21 @@ __global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict
             const T* ra = wae + (size_t)r * K;
             const T* rb = DUAL ? wbe + (size_t)r * K : nullptr;
             if (VEC) {
-                // two 16-byte pieces of the row (and of its twin) are requested before either is used
-                for (int i = lane * P; i < K; i += 64 * P) {
-                    float va[2][P], vb[2][P];
+                // 16-byte pieces of weights requested before any is used: two of the row and two of its twin, four of a lone first-stage
+                // row; the second stage keeps two (its order of summation is what the routed models' recorded results were made with)
+                constexpr int NQ = MODE == 2 ? 4 : 2;
+                for (int i = lane * P; i < K; i += 32 * NQ * P) {
+                    float va[NQ][P], vb[DUAL ? NQ : 1][P];
 #pragma unroll
-                    for (int q2 = 0; q2 < 2; ++q2) {
+                    for (int q2 = 0; q2 < NQ; ++q2) {
                         const int at = i + q2 * 32 * P;
                         if (at < K) {
                             load_pack<T>(ra + at, va[q2]);
-                            if (DUAL) load_pack<T>(rb + at, vb[q2]);
+                            if (DUAL) load_pack<T>(rb + at, vb[DUAL ? q2 : 0]);
                         }
                     }
 #pragma unroll
-                    for (int q2 = 0; q2 < 2; ++q2) {
+                    for (int q2 = 0; q2 < NQ; ++q2) {
                         const int at = i + q2 * 32 * P;
                         if (at < K) {
 #pragma unroll
@@ -615,7 +617,7 @@ __global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict
 #pragma unroll
                                 for (int k = 0; k < P; ++k) {
                                     a[u] = fmaf(va[q2][k], xv[k], a[u]);
-                                    if (DUAL) b[u] = fmaf(vb[q2][k], xv[k], b[u]);
+                                    if (DUAL) b[u] = fmaf(vb[DUAL ? q2 : 0][k], xv[k], b[u]);
                                 }
                             }
                         }
@@ -1192,22 +1194,29 @@ B200H_API int b200h_short_conv(const void* u, int64_t ld, const void* w, const v
 }
 
 B200H_API int b200h_ssm_scan(const void* xbc, const void* dt, int64_t ld_dt, const void* dt_bias, const void* a_log, const void* skip,
-                             void* state, int64_t slot_stride, const void* cu_q, const void* seq_slot, int batch, int heads, int vdim,
-                             int nstate, int groups, void* out, int dtype, void* stream)
+                             void* state, int64_t slot_stride, const void* cu_q, const void* seq_slot, int n, int batch, int heads, int vdim,
+                             int nstate, int groups, void* steps, void* out, int dtype, void* stream)
 {
-    if (!xbc || !dt || !dt_bias || !a_log || !skip || !state || !cu_q || !seq_slot || !out || batch <= 0 || heads <= 0 || vdim <= 0 ||
-        nstate <= 0 || groups <= 0 || heads % groups)
+    if (!xbc || !dt || !dt_bias || !a_log || !skip || !state || !cu_q || !seq_slot || !steps || !out || n < 0 || batch <= 0 || heads <= 0 ||
+        vdim <= 0 || nstate <= 0 || groups <= 0 || heads % groups)
         return fail(B200H_ERR_INVALID_ARG, "ssm_scan: bad arguments");
     if (nstate > 256) return fail(B200H_ERR_UNSUPPORTED, "ssm_scan: state <= 256");
+    if (n == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    const int cols = vdim < 8 ? vdim : 8;
-    const dim3 grid((vdim + cols - 1) / cols, heads, batch), block(32, cols);
+    const int64_t count = (int64_t)n * heads;
+    B200H_DISPATCH_T(dtype, ssm_steps_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, st>>>((const T*)dt, ld_dt, (const float*)dt_bias,
+                                                                                               (const float*)a_log, heads, count, (float2*)steps));
+    // two value columns per warp where the head has an even number of them (B and C are read once for both)
+    const int nc = vdim % 2 == 0 ? 2 : 1, units = vdim / nc, warps = units < 8 ? units : 8;
+    const dim3 grid((units + warps - 1) / warps, heads, batch), block(32, warps);
     const int nw = (nstate + 31) / 32;
-#define B200H_SCAN(NW)                                                                                                                   \
-    ssm_scan_kernel<T, NW><<<grid, block, 0, st>>>((const float*)xbc, (const T*)dt, ld_dt, (const float*)dt_bias, (const float*)a_log,    \
-                                                   (const float*)skip, (float*)state, slot_stride, (const int*)cu_q, (const int*)seq_slot, \
-                                                   heads, vdim, nstate, groups, (float*)out)
-    B200H_DISPATCH_T(dtype, if (nw <= 1) B200H_SCAN(1); else if (nw <= 2) B200H_SCAN(2); else if (nw <= 4) B200H_SCAN(4); else B200H_SCAN(8));
+#define B200H_SCAN(NW, NC)                                                                                                               \
+    ssm_scan_kernel<NW, NC><<<grid, block, 0, st>>>((const float*)xbc, (const float2*)steps, (const float*)skip, (float*)state, slot_stride, \
+                                                    (const int*)cu_q, (const int*)seq_slot, heads, vdim, nstate, groups, (float*)out)
+#define B200H_SCAN_NW(NC) \
+    do { if (nw <= 1) B200H_SCAN(1, NC); else if (nw <= 2) B200H_SCAN(2, NC); else if (nw <= 4) B200H_SCAN(4, NC); else B200H_SCAN(8, NC); } while (0)
+    if (nc == 2) B200H_SCAN_NW(2); else B200H_SCAN_NW(1);
+#undef B200H_SCAN_NW
 #undef B200H_SCAN
     return launched("ssm_scan");
 }

@@ -47,36 +47,54 @@ __global__ void short_conv_state_kernel(const T* __restrict__ u, int64_t ld, flo
 
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
-// Per head S <- a_t S + dt_t B_t x_t^T, y_t = S^T C_t + D x_t with dt_t = softplus(dt + dt_bias), a_t = exp(-exp(A_log) dt_t).
-// The columns of S (one per value channel) are independent: one warp owns one (sequence, head, value column), lane l keeps
-// rows l, l + 32, ... of that column in registers and walks the sequence's rows of this step in order.
-// xbc: float [n, inner + 2 * groups * N] = x | B | C after convolution and silu; dt: T with row stride ld_dt, one column per head.
-template <typename T, int NW>
-__global__ void ssm_scan_kernel(const float* __restrict__ xbc, const T* __restrict__ dt, int64_t ld_dt, const float* __restrict__ dt_bias,
-                                const float* __restrict__ a_log, const float* __restrict__ skip, float* __restrict__ state,
-                                int64_t slot_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int vdim,
-                                int N, int groups, float* __restrict__ out)
+// steps[t, h] = (dt, a) with dt = softplus(dt_raw[t, h] + dt_bias[h]) and a = exp(-exp(A_log[h]) * dt): computed once per (row, head)
+// instead of once per value column of the head.
+template <typename T>
+__global__ void ssm_steps_kernel(const T* __restrict__ dt, int64_t ld_dt, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                 int heads, int64_t count, float2* __restrict__ steps)
 {
-    const int col = blockIdx.x * blockDim.y + threadIdx.y, h = blockIdx.y, s = blockIdx.z, lane = threadIdx.x;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const int64_t t = i / heads;
+    const int h = (int)(i - t * heads);
+    const float d = softplus_f(to_f(dt[t * ld_dt + h]) + dt_bias[h]);
+    steps[i] = make_float2(d, expf(-expf(a_log[h]) * d));
+}
+
+// Per head S <- a_t S + dt_t B_t x_t^T, y_t = S^T C_t + D x_t, (dt_t, a_t) from ssm_steps_kernel.
+// The columns of S (one per value channel) are independent: one warp owns NC value columns of one (sequence, head), lane l keeps
+// rows l, l + 32, ... of those columns in registers and walks the sequence's rows of this step in order; B_t and C_t are read once
+// for the warp's NC columns.
+// xbc: float [n, inner + 2 * groups * N] = x | B | C after convolution and silu.
+template <int NW, int NC>
+__global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float2* __restrict__ steps, const float* __restrict__ skip,
+                                float* __restrict__ state, int64_t slot_stride, const int* __restrict__ cu_q,
+                                const int* __restrict__ seq_slot, int heads, int vdim, int N, int groups, float* __restrict__ out)
+{
+    const int col = (blockIdx.x * blockDim.y + threadIdx.y) * NC, h = blockIdx.y, s = blockIdx.z, lane = threadIdx.x;
     if (col >= vdim) return;
     const int first = cu_q[s], last = cu_q[s + 1];
     if (first == last) return;
     const int inner = heads * vdim, channels = inner + 2 * groups * N, grp = h / (heads / groups);
     float* sp = state + (int64_t)seq_slot[s] * slot_stride + ((size_t)h * vdim + col) * N;
-    float st[NW];
+    float st[NC][NW];
 #pragma unroll
-    for (int i = 0; i < NW; ++i) { const int d = i * 32 + lane; st[i] = d < N ? sp[d] : 0.f; }
-    const float rate = expf(a_log[h]), bias = dt_bias[h], dskip = skip[h];
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int i = 0; i < NW; ++i) { const int d = i * 32 + lane; st[c][i] = d < N ? sp[(size_t)c * N + d] : 0.f; }
+    const float dskip = skip[h];
     const size_t x_at = (size_t)h * vdim + col, b_at = (size_t)inner + (size_t)grp * N, c_at = b_at + (size_t)groups * N;
-    // four rows at a time: their loads, step sizes and decays do not depend on the state, only the four updates are in order
+    // four rows at a time: their loads do not depend on the state, only the four updates are in order
     for (int t0 = first; t0 < last; t0 += 4) {
-        float ba[4][NW], ca[4][NW], xa[4], da[4], aa[4];
+        float ba[4][NW], ca[4][NW], xa[4][NC];
+        float2 sd[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             if (t0 + u < last) {                      // a step of one row (decode) loads one row
                 const float* row = xbc + (size_t)(t0 + u) * channels;
-                xa[u] = row[x_at];
-                da[u] = to_f(dt[(size_t)(t0 + u) * ld_dt + h]);
+#pragma unroll
+                for (int c = 0; c < NC; ++c) xa[u][c] = row[x_at + c];
+                sd[u] = steps[(size_t)(t0 + u) * heads + h];
 #pragma unroll
                 for (int i = 0; i < NW; ++i) {
                     const int d = i * 32 + lane;
@@ -88,27 +106,30 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const T* __restri
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             if (t0 + u < last) {
-                da[u] = softplus_f(da[u] + bias);
-                aa[u] = expf(-rate * da[u]);
-            }
-        }
+                float part[NC];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            if (t0 + u < last) {
-                const float dx = da[u] * xa[u];
-                float part = 0.f;
+                for (int c = 0; c < NC; ++c) {
+                    const float dx = sd[u].x * xa[u][c];
+                    part[c] = 0.f;
 #pragma unroll
-                for (int i = 0; i < NW; ++i) {
-                    st[i] = fmaf(aa[u], st[i], ba[u][i] * dx);              // rows past N hold zeros and stay zero
-                    part = fmaf(st[i], ca[u][i], part);
+                    for (int i = 0; i < NW; ++i) {
+                        st[c][i] = fmaf(sd[u].y, st[c][i], ba[u][i] * dx);          // rows past N hold zeros and stay zero
+                        part[c] = fmaf(st[c][i], ca[u][i], part[c]);
+                    }
                 }
-                part = warp_sum(part);
-                if (lane == 0) out[(size_t)(t0 + u) * inner + x_at] = part + dskip * xa[u];
+#pragma unroll
+                for (int c = 0; c < NC; ++c) part[c] = warp_sum(part[c]);
+                if (lane == 0) {
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) out[(size_t)(t0 + u) * inner + x_at + c] = part[c] + dskip * xa[u][c];
+                }
             }
         }
     }
 #pragma unroll
-    for (int i = 0; i < NW; ++i) { const int d = i * 32 + lane; if (d < N) sp[d] = st[i]; }
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int i = 0; i < NW; ++i) { const int d = i * 32 + lane; if (d < N) sp[(size_t)c * N + d] = st[c][i]; }
 }
 
 // out[t] = unit_rms_per_group(y[t] * silu(gate[t])) * w as T: the gate comes before the norm; `groups` equal parts of `count` columns.

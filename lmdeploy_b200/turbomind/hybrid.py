@@ -310,9 +310,10 @@ class HybridModel:
         s, W = self.spec, self.spec.width
         pre = s.block == "pre_norm"
         par = s.block == "parallel"
-        out = {"embed": (s.vocab, W), "final.norm": (W,)}
+        out = {"embed": (s.vocab, W)}
         if not s.tied_head:
             out["head"] = (s.vocab, W)
+        out["final.norm"] = (W,)
         if s.max_positions:
             out["pos"] = (s.max_positions, W)
         if s.loop is not None:
@@ -365,9 +366,9 @@ class HybridModel:
                     continue
                 out[p + "mlp.router"] = (f.experts, W)
                 for e in range(f.experts):
-                    out.update({f"{p}mlp.e{e}.up": (f.ff, W), f"{p}mlp.e{e}.down": (W, f.ff)})
                     if f.act == "silu_gate":
                         out[f"{p}mlp.e{e}.gate"] = (f.ff, W)
+                    out.update({f"{p}mlp.e{e}.up": (f.ff, W), f"{p}mlp.e{e}.down": (W, f.ff)})
         return out
 
     # ------------------------------------------------------------------ step
@@ -708,11 +709,12 @@ class HybridModel:
                                          c.seq_slot.data_ptr(), xbc.data_ptr(), n, c.batch, m.conv_channels, m.conv_taps, self.dt, st),
                     "short_conv")
         o = torch.empty(n, m.inner, dtype=torch.float32, device=dev)
+        steps = torch.empty(n, m.heads, 2, dtype=torch.float32, device=dev)
         with self.timed("state-space scan"):
             H.check(lib.b200h_ssm_scan(xbc.data_ptr(), base + es * (m.inner + m.conv_channels), ld, w[p + "dt_bias"].data_ptr(),
                                        w[p + "A_log"].data_ptr(), w[p + "D"].data_ptr(), c.state.ptr(self.mix_off[r]), stride,
-                                       c.cu_q.data_ptr(), c.seq_slot.data_ptr(), c.batch, m.heads, m.vdim, m.state, m.groups,
-                                       o.data_ptr(), self.dt, st), "ssm_scan")
+                                       c.cu_q.data_ptr(), c.seq_slot.data_ptr(), n, c.batch, m.heads, m.vdim, m.state, m.groups,
+                                       steps.data_ptr(), o.data_ptr(), self.dt, st), "ssm_scan")
         y = torch.empty(n, m.inner, dtype=self.T, device=dev)
         with self.timed("gate + grouped norm"):
             H.check(lib.b200h_gate_group_norm(o.data_ptr(), base, ld, w[p + "mixnorm"].data_ptr(), n, m.inner, m.norm_groups,

@@ -354,10 +354,11 @@ class EmulatedHybridLib:
         _f(out, n, channels)[:] = y * _sigmoid(y) if act == 1 else y
         return 0
 
-    def b200h_ssm_scan(self, xbc, dt, ld_dt, dt_bias, a_log, skip, state, slot_stride, cu_q, seq_slot, batch, heads, vdim, nstate, groups,
-                       out, dtype, stream):
+    def b200h_ssm_scan(self, xbc, dt, ld_dt, dt_bias, a_log, skip, state, slot_stride, cu_q, seq_slot, n, batch, heads, vdim, nstate,
+                       groups, steps, out, dtype, stream):
         cu, slots = _i(cu_q, batch + 1), _i(seq_slot, batch)
-        n, inner, gn = int(cu[batch]), heads * vdim, groups * nstate
+        assert n == int(cu[batch]) and steps
+        inner, gn = heads * vdim, groups * nstate
         X = _f(xbc, n, inner + 2 * gn)
         DT = _rows(dt, n, ld_dt, heads) + _f(dt_bias, heads)
         DT = (np.maximum(DT, 0) + np.log1p(np.exp(-np.abs(DT)))).astype(np.float32)

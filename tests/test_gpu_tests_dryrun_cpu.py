@@ -79,6 +79,9 @@ def cpu_as_cuda(monkeypatch, lib):
     ref = AnyLib()
     for mod, fn in ((ref_lib, "load"), (ref_lib, "load_norm"), (ref_lib, "load_prefill"), (ref_gemm_lib, "load")):
         monkeypatch.setattr(mod, fn, lambda _ref=ref: _ref)
+    # the stand-in replaces the reference's libraries whether or not they were built on this machine
+    for mod, fn in ((ref_lib, "available"), (ref_lib, "norm_available"), (ref_lib, "prefill_available"), (ref_gemm_lib, "available")):
+        monkeypatch.setattr(mod, fn, lambda: True)
     rec.ref = ref
     return rec
 
