@@ -593,8 +593,8 @@ __global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict
             const T* ra = wae + (size_t)r * K;
             const T* rb = DUAL ? wbe + (size_t)r * K : nullptr;
             if (VEC) {
-                // 16-byte pieces of weights requested before any is used: two of the row and two of its twin, four of a lone first-stage
-                // row; the second stage keeps two (its order of summation is what the routed models' recorded results were made with)
+                // 16-byte pieces of weights requested before any is used: two of the row and two of its twin, or four of a lone
+                // first-stage row; the second stage requests two
                 constexpr int NQ = MODE == 2 ? 4 : 2;
                 for (int i = lane * P; i < K; i += 32 * NQ * P) {
                     float va[NQ][P], vb[DUAL ? NQ : 1][P];
@@ -1235,7 +1235,7 @@ B200H_API int b200h_gate_group_norm(const void* y, const void* gate, int64_t ld_
 B200H_API int b200h_conv_rope_prep(const b200h_conv_prep_args* a)
 {
     if (!a || !a->qk || !a->conv || !a->state || !a->qn || !a->tok_seq || !a->tok_pos || !a->cu_q || !a->seq_slot || !a->block_ptrs ||
-        !a->cu_blocks || a->heads <= 0 || a->kv_heads <= 0 || a->dim <= 0 || a->dim % 2 || a->block_len <= 0 || a->batch <= 0)
+        !a->cu_blocks || a->heads <= 0 || a->kv_heads <= 0 || a->dim <= 0 || a->block_len <= 0 || a->batch <= 0)
         return fail(B200H_ERR_INVALID_ARG, "conv_rope_prep: bad arguments");
     if (a->taps < 1 || a->taps > B200H_MAX_TAPS) return fail(B200H_ERR_UNSUPPORTED, "conv_rope_prep: taps 1..16");
     if (a->rot.pairs < 0 || 2 * a->rot.pairs > a->dim || (a->rot.pairs && !a->rot.freqs))

@@ -72,36 +72,38 @@ __global__ void conv_rope_prep_kernel(const T* __restrict__ qk, int64_t ld, cons
     const int at = pos % block_len;
     T* k_dst = reinterpret_cast<T*>(page) + (size_t)at * GD;
     T* v_dst = reinterpret_cast<T*>(page + v_off) + (size_t)at * GD;
-    for (int i = threadIdx.x; i < channels / 2; i += blockDim.x) {
-        const int c = 2 * i;
+    // one item per (head, pair of dimensions); a head of odd size ends in a lone dimension, which never turns
+    const int per_head = (dim + 1) / 2;
+    for (int i = threadIdx.x; i < (heads + kv_heads) * per_head; i += blockDim.x) {
+        const int hh = i / per_head, pair = i - hh * per_head, c = hh * dim + 2 * pair;
+        const bool two = 2 * pair + 1 < dim;
         float a = 0.f, b = 0.f;
         for (int j = 0; j < taps; ++j) {
             const int src = local - (taps - 1) + j;
-            float ua, ub;
+            float ua, ub = 0.f;
             if (src >= 0) {
                 const T* row = qk + (size_t)(first + src) * ld + c;
                 ua = to_f(row[0]);
-                ub = to_f(row[1]);
+                if (two) ub = to_f(row[1]);
             } else {
                 const float* row = st + (size_t)(src + taps - 1) * channels + c;
                 ua = row[0];
-                ub = row[1];
+                if (two) ub = row[1];
             }
             a = fmaf(conv[c * taps + j], ua, a);
-            b = fmaf(conv[(c + 1) * taps + j], ub, b);
+            if (two) b = fmaf(conv[(c + 1) * taps + j], ub, b);
         }
         if (c >= HD) {
             v_dst[c - HD] = from_f<T>(a);
-            v_dst[c - HD + 1] = from_f<T>(b);
+            if (two) v_dst[c - HD + 1] = from_f<T>(b);
         }
-        const int pair = (c % dim) / 2;
-        if (pair < rot.pairs) {
+        if (pair < rot.pairs) {                          // 2 * rot.pairs <= dim: a turning pair is always whole
             const float ra = a * cs[pair] - b * sn[pair], rb = b * cs[pair] + a * sn[pair];
             a = ra;
             b = rb;
         }
         buf[c] = a;
-        buf[c + 1] = b;
+        if (two) buf[c + 1] = b;
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;

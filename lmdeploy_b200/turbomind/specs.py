@@ -362,8 +362,8 @@ def _lifuzen_mixer(kind, m):
         if vdim != dim:
             raise ValueError(f"vdim {vdim} != dim {dim}: the values of this attention are its keys")
         rot = RotarySpec(int(m["rot"]["dims"]), float(m["rot"]["base"]))
-        if rot.dims > dim or rot.dims % 2 or dim % 2:
-            raise ValueError(f"rot.dims {rot.dims} does not fit dim {dim} (both even)")
+        if rot.dims > dim or rot.dims % 2:
+            raise ValueError(f"rot.dims {rot.dims} (even) does not fit dim {dim}")
         return ConvAttentionSpec(heads, kv_heads, dim, vdim, float(m["scale"]), int(m["conv"]), rot)
     if kind == "mamba2":
         s = SsmSpec(int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"]), int(m["norm_groups"]), int(m["conv"]))

@@ -139,7 +139,7 @@ def other_sizes(make, tol):
 
 def wider_sizes(make, tol):
     """Sizes of the order of a real layer's heads: 16 query heads on 2 key/value heads, head dimensions of 64 and 128 (16-byte
-    key reads) and an odd-sized one (scalar reads), a state of 128 with value heads of 64, expert widths that are and are not
+    key reads) and an odd one (scalar reads, a lone last dimension), a state of 128 with value heads of 64, expert widths that are and are not
     multiples of eight (16-byte and scalar weight reads), prompts long enough for the grouped expert GEMMs and for key ranges."""
     A, M, E = LC.attention, LC.ssm, LC.moe
     stacks = [
@@ -148,7 +148,7 @@ def wider_sizes(make, tol):
              width=128, vocab=77, loop=(0, 2, 2)),
         dict(layers=[dict(A(heads=4, kv_heads=4, dim=128, taps=2, rot_dims=64, scale=0.09), mlp=None),
                      dict(M(heads=5, vdim=9, state=17, groups=1, norm_groups=5, taps=3), mlp=E(experts=6, top=2, ff=21)),
-                     dict(A(heads=3, kv_heads=1, dim=34, taps=3, rot_dims=10, scale=0.2), mlp=E(experts=2, top=1, ff=32))],
+                     dict(A(heads=3, kv_heads=1, dim=33, taps=3, rot_dims=10, scale=0.2), mlp=E(experts=2, top=1, ff=32))],
              width=66, vocab=50, loop=None),
     ]
     for k, kw in enumerate(stacks):
