@@ -1,6 +1,7 @@
 /* C ABI of libb200hybrid.so: the operators of hybrid decoders (latent attention with a sink, decayed linear attention,
  * routed experts, grouped RMS norm, short causal convolution, depth-weighted residual history; windowed attention with
- * grouped key/value heads, residual add + RMS norm, learned positions) for sm_100a.
+ * grouped key/value heads, residual add + RMS norm, learned positions; parallel blocks with two norms, convolved rotary
+ * attention whose values are its keys, a selective state-space mixer, sigmoid-routed experts) for sm_100a.
  *
  * Conventions shared by all entries: raw device pointers, sizes as int, `stream` a cudaStream_t, return 0 on success, a
  * negative b200h_status for refused arguments, a positive cudaError_t for a failed launch; b200h_last_error() says why.

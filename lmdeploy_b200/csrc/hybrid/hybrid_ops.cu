@@ -1,5 +1,7 @@
 // Operators of hybrid decoders (latent attention with a sink, decayed linear attention, routed experts, grouped RMS norm,
-// short causal convolution, depth-weighted residual history) behind a C ABI of their own: libb200hybrid.so.
+// short causal convolution, depth-weighted residual history; window_attention.cuh: pre-norm blocks and windowed attention;
+// ssm.cuh, parallel_block.cuh: the state-space mixer, parallel blocks and convolved rotary attention) behind a C ABI of
+// their own: libb200hybrid.so.
 //
 // Number formats.  T is the activation / weight type of the matrix products (float or bf16).  Everything the designs want in
 // 32 bits is float here whatever T is: the residual stream and its history, every norm, rotary angles (double), attention
