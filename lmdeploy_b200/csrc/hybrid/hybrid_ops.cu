@@ -565,14 +565,14 @@ __device__ __forceinline__ void load_pack<float>(const float* p, float (&v)[4])
     v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
 }
 
-template <typename T, int MODE, bool VEC>
+template <typename T, int MODE, bool VEC, int TILE>
 __global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict__ x, int x_div, const T* __restrict__ wa, const T* __restrict__ wb,
                                    const int* __restrict__ counts, const int* __restrict__ lists, int entries,
                                    const float* __restrict__ wts, int K, int R, void* __restrict__ out_)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr bool DUAL = MODE == 1;
-    T* xs = reinterpret_cast<T*>(smem_raw);                     // [kExpertTile][K]
+    T* xs = reinterpret_cast<T*>(smem_raw);                     // [TILE][K]
     const int e = blockIdx.y, r0 = blockIdx.x * kExpertRows;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int count = counts[e];
@@ -580,18 +580,18 @@ __global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict
     const T* wae = wa + (size_t)e * R * K;
     const T* wbe = DUAL ? wb + (size_t)e * R * K : nullptr;
     constexpr int P = Pack<T>::N;
-    for (int base = 0; base < count; base += kExpertTile) {
-        const int live = min(kExpertTile, count - base);
+    for (int base = 0; base < count; base += TILE) {
+        const int live = min(TILE, count - base);
         __syncthreads();
-        for (int u = 0; u < kExpertTile; ++u) {
+        for (int u = 0; u < TILE; ++u) {
             const T* src = u < live ? x + (size_t)(list[base + u] / x_div) * K : nullptr;
             for (int i = threadIdx.x; i < K; i += blockDim.x) xs[(size_t)u * K + i] = src ? src[i] : from_f<T>(0.f);
         }
         __syncthreads();
         for (int r = r0 + warp; r < min(R, r0 + kExpertRows); r += nw) {
-            float a[kExpertTile], b[kExpertTile];
+            float a[TILE], b[TILE];
 #pragma unroll
-            for (int u = 0; u < kExpertTile; ++u) a[u] = b[u] = 0.f;
+            for (int u = 0; u < TILE; ++u) a[u] = b[u] = 0.f;
             const T* ra = wae + (size_t)r * K;
             const T* rb = DUAL ? wbe + (size_t)r * K : nullptr;
             if (VEC) {
@@ -613,7 +613,7 @@ __global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict
                         const int at = i + q2 * 32 * P;
                         if (at < K) {
 #pragma unroll
-                            for (int u = 0; u < kExpertTile; ++u) {
+                            for (int u = 0; u < TILE; ++u) {
                                 float xv[P];
                                 load_pack<T>(xs + (size_t)u * K + at, xv);
 #pragma unroll
@@ -629,7 +629,7 @@ __global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict
                 for (int i = lane; i < K; i += 32) {
                     const float va = to_f(ra[i]), vb = DUAL ? to_f(rb[i]) : 0.f;
 #pragma unroll
-                    for (int u = 0; u < kExpertTile; ++u) {
+                    for (int u = 0; u < TILE; ++u) {
                         const float xv = to_f(xs[(size_t)u * K + i]);
                         a[u] = fmaf(va, xv, a[u]);
                         if (DUAL) b[u] = fmaf(vb, xv, b[u]);
@@ -637,14 +637,14 @@ __global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict
                 }
             }
 #pragma unroll
-            for (int u = 0; u < kExpertTile; ++u) {
+            for (int u = 0; u < TILE; ++u) {
                 a[u] = warp_sum(a[u]);
                 if (DUAL) b[u] = warp_sum(b[u]);
             }
             if (lane < live) {
                 float va = 0.f, vb = 0.f;
 #pragma unroll
-                for (int u = 0; u < kExpertTile; ++u)
+                for (int u = 0; u < TILE; ++u)
                     if (u == lane) { va = a[u]; vb = b[u]; }
                 const int entry = list[base + lane];
                 const float wt = wts ? wts[entry] : 1.0f;
@@ -956,12 +956,19 @@ static void launch_expert_rows(const b200h_expert_args* a, cudaStream_t st)
     // the router's score goes to the first product when it scales the expert's input, to the last one otherwise
     const float* w_in = a->scale_input ? (const float*)a->wts : nullptr;
     const float* w_out = a->scale_input ? nullptr : (const float*)a->wts;
-#define B200H_ROWS(MODE, VEC, GRID, SM, X, DIV, WA, WB, WTS, K, R, OUT)                                                                 \
+    // eight entries share a pass over an expert's weight rows; four where eight staged input rows would leave room for fewer than
+    // three blocks per SM (the per-entry sums are the same either way)
+#define B200H_ROWS_T(MODE, VEC, TILE, GRID, SM, X, DIV, WA, WB, WTS, K, R, OUT)                                                         \
     do {                                                                                                                               \
         if ((SM) > 48 * 1024)                                                                                                          \
-            cudaFuncSetAttribute(expert_rows_kernel<T, MODE, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SM));            \
-        expert_rows_kernel<T, MODE, VEC><<<GRID, 256, SM, st>>>((const T*)(X), DIV, (const T*)(WA), (const T*)(WB), (const int*)a->counts, \
-                                                               (const int*)a->lists, entries, WTS, K, R, OUT);                          \
+            cudaFuncSetAttribute(expert_rows_kernel<T, MODE, VEC, TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SM));      \
+        expert_rows_kernel<T, MODE, VEC, TILE><<<GRID, 256, SM, st>>>((const T*)(X), DIV, (const T*)(WA), (const T*)(WB),              \
+                                                                     (const int*)a->counts, (const int*)a->lists, entries, WTS, K, R, OUT); \
+    } while (0)
+#define B200H_ROWS(MODE, VEC, GRID, SM, X, DIV, WA, WB, WTS, K, R, OUT)                                                                 \
+    do {                                                                                                                               \
+        if ((SM) > 72 * 1024) B200H_ROWS_T(MODE, VEC, 4, GRID, (SM) / 2, X, DIV, WA, WB, WTS, K, R, OUT);                               \
+        else B200H_ROWS_T(MODE, VEC, 8, GRID, SM, X, DIV, WA, WB, WTS, K, R, OUT);                                                      \
     } while (0)
     if (a->act == 1) {
         if (vec) B200H_ROWS(2, true, g_up, sm_up, a->x, a->top, a->up, nullptr, w_in, a->width, a->ff, a->mid);
@@ -973,6 +980,7 @@ static void launch_expert_rows(const b200h_expert_args* a, cudaStream_t st)
     if (vec) B200H_ROWS(0, true, g_down, sm_down, a->mid, 1, a->down, nullptr, w_out, a->ff, a->width, a->out);
     else B200H_ROWS(0, false, g_down, sm_down, a->mid, 1, a->down, nullptr, w_out, a->ff, a->width, a->out);
 #undef B200H_ROWS
+#undef B200H_ROWS_T
 }
 
 B200H_API int b200h_experts(const b200h_expert_args* a)
@@ -982,7 +990,7 @@ B200H_API int b200h_experts(const b200h_expert_args* a)
         return fail(B200H_ERR_INVALID_ARG, "experts: bad arguments");
     if (a->n == 0) return 0;
     const size_t widest = (size_t)kExpertTile * (a->width > a->ff ? a->width : a->ff) * (a->dtype == B200H_F32 ? 4 : 2);
-    if (widest > 200 * 1024) return fail(B200H_ERR_UNSUPPORTED, "experts: eight rows of width / ff exceed shared memory");
+    if (widest / 2 > 200 * 1024) return fail(B200H_ERR_UNSUPPORTED, "experts: four rows of width / ff exceed shared memory");
     if ((size_t)a->experts * sizeof(int) > 48 * 1024) return fail(B200H_ERR_UNSUPPORTED, "experts: more than 12288 experts");
     cudaStream_t st = (cudaStream_t)a->stream;
     expert_lists_kernel<<<1, 1024, a->experts * sizeof(int), st>>>((const int*)a->ids, a->n * a->top, a->experts, (int*)a->counts,
