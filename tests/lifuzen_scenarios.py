@@ -306,8 +306,10 @@ def routed_experts_alone(make, tol):
     """Sigmoid scores, the `top` largest, each expert fed score * h: few rows (expert-major kernels) and many (grouped GEMMs)
     against the oracle; scores well apart from one so that scaling the input (squared by the activation) differs from
     scaling the output."""
-    for top, experts, ff, n in ((2, 5, 24, 6), (1, 3, 10, 5), (3, 3, 16, 200), (2, 4, 9, 260)):
-        cfg = LC.config(layers=[dict(LC.ssm(), mlp=LC.moe(experts=experts, top=top, ff=ff))], loop=None)
+    # the last two: rows so long that eight of them (as float) would crowd an SM's shared memory, first in the up stage, then in the down stage
+    for top, experts, ff, n, width in ((2, 5, 24, 6, 48), (1, 3, 10, 5, 48), (3, 3, 16, 200, 48), (2, 4, 9, 260, 48), (2, 3, 24, 11, 2400),
+                                       (2, 2, 2400, 11, 48)):
+        cfg = LC.config(layers=[dict(LC.ssm(), mlp=LC.moe(experts=experts, top=top, ff=ff))], loop=None, width=width)
         w = LC.random_tensors(cfg, seed=34 + top)
         w["l0.mlp.router"] = (0.15 * w["l0.mlp.router"]).to(torch.bfloat16).float()       # logits of order one: scores between 0 and 1
         eng = make(cfg, w)
@@ -318,7 +320,7 @@ def routed_experts_alone(make, tol):
         out = model.routed_experts(0, None, h.to(model.device, model.T).contiguous(), n)
         ids, wts = model.last_routing
         assert float(wts.min()) > 0 and float(wts.max()) < 1 and float((wts - 0.5).abs().max()) > 0.2
-        _close(out.sum(1).cpu(), want, tol, f"experts top {top} of {experts}, {n} rows")
+        _close(out.sum(1).cpu(), want, tol, f"experts top {top} of {experts}, {n} rows, width {width}, ff {ff}")
 
 
 def residual_and_two_norms(make, tol):
