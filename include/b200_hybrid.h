@@ -1,7 +1,9 @@
 /* C ABI of libb200hybrid.so: the operators of hybrid decoders (latent attention with a sink, decayed linear attention,
  * routed experts, grouped RMS norm, short causal convolution, depth-weighted residual history; windowed attention with
  * grouped key/value heads, residual add + RMS norm, learned positions; parallel blocks with two norms, convolved rotary
- * attention whose values are its keys, a selective state-space mixer, sigmoid-routed experts) for sm_100a.
+ * attention whose values are its keys, a selective state-space mixer, sigmoid-routed experts; parallel blocks with one norm
+ * and a token shift, two mixers side by side, chunked rotary attention with scores mixed across heads, a recurrence with a
+ * decay per key channel and token, a router that chooses among groups of experts) for sm_100a.
  *
  * Conventions shared by all entries: raw device pointers, sizes as int, `stream` a cudaStream_t, return 0 on success, a
  * negative b200h_status for refused arguments, a positive cudaError_t for a failed launch; b200h_last_error() says why.
@@ -18,6 +20,56 @@
 #define B200H_API extern "C" __attribute__((visibility("default")))
 #else
 #define B200H_API
+
+/* ---- parallel blocks with one norm and a token shift, side-by-side mixers, recurrence with a decay per channel and token ---- */
+
+/* out[t] = table[tokens[t]] + second[row] (float), row = (previous token * mul_prev + tokens[t] * mul_cur) mod buckets, or `buckets`
+ * (the table's last row) at position 0.  The token before an entry's first row is the int at prev + seq_slot[s] * slot_stride (in
+ * a float's place), which then becomes the entry's last token of this step. */
+B200H_API int b200h_embed_hashed(const void* tokens, const void* table, const void* second, int buckets, int mul_prev, int mul_cur, void* prev,
+                                 int64_t slot_stride, const void* tok_seq, const void* tok_pos, const void* cu_q, const void* seq_slot,
+                                 void* out, int n, int batch, int width, int dtype, void* stream);
+
+/* x[t] += branch_scale * (left[t] / rms(left[t]) * wl + right[t] / rms(right[t]) * wr) + sum_p ff[t, p]; then, if w is given,
+ * hf[t] = x[t] / rms(x[t]) * w (float) and h[t] the same as T.  left, right: T [n, width] (both or neither) with wl, wr float
+ * [width]; ff: T (or float when ff_is_f32) [n, parts, width] or NULL; h, hf optional. */
+B200H_API int b200h_branch_residual_norm(void* x, const void* left, const void* right, const void* wl, const void* wr, float branch_scale,
+                                         const void* ff, int ff_is_f32, int parts, const void* w, int n, int width, float eps, void* h,
+                                         void* hf, int dtype, void* stream);
+
+/* Token shift of normed rows h (float [n, width]): a[t] = h[t] + (h[t-1] - h[t]) * shift (shift float [width] or NULL: a = h), and
+ * for m < nmu blends[m][t] = a[t] + (a[t-1] - a[t]) * mu[m] (mu float [nmu, width]; a, blends T, blends [nmu, n, width]; a optional).
+ * The rows before an entry's first come from its state (float [2, width] = its last h and a at state + seq_slot[s] * slot_stride;
+ * zeros at a sequence's start), which is then advanced by the step. */
+B200H_API int b200h_token_shift(const void* h, const void* shift, const void* mu, int nmu, void* state, int64_t slot_stride,
+                                const void* tok_seq, const void* cu_q, const void* seq_slot, int n, int batch, int width, void* a,
+                                void* blends, int dtype, void* stream);
+
+/* Per head, S a [dim, vdim] float matrix per sequence:  w_t = exp(-exp(d_t + w0)) per key channel;
+ * out_t = (S + diag(bonus) k_t v_t^T)^T r_t;  S <- diag(w_t) S + k_t v_t^T.  r, k (heads * dim columns) and v (heads * vdim) are T
+ * with row stride ld; d float [n, heads * dim]; w0, bonus float [heads * dim]; state float [heads, vdim, dim] at state + seq_slot[s] *
+ * slot_stride, read and advanced; decay: float [n, heads * dim] scratch; out float [n, heads * vdim]. */
+B200H_API int b200h_channel_decay_scan(const void* r, const void* k, const void* v, int64_t ld, const void* d, const void* w0,
+                                       const void* bonus, void* state, int64_t slot_stride, const void* cu_q, const void* seq_slot, int n,
+                                       int batch, int heads, int dim, int vdim, void* decay, void* out, int dtype, void* stream);
+
+/* y[t] = unit_rms_per_group(o[t]) * w * act(gate[t]) as T: the norm BEFORE the gate; o float [n, count], `groups` equal parts,
+ * gate T with row stride ld_gate; act 0 sigmoid, 1 silu. */
+B200H_API int b200h_group_norm_gate(const void* o, const void* w, const void* gate, int64_t ld_gate, int n, int count, int groups, int act,
+                                    float eps, void* y, int dtype, void* stream);
+
+/* x <- z > 0 ? softplus(p) z^2 + z / 2 : (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 in place (T); params = {p, q} floats on the device. */
+B200H_API int b200h_xielu(void* x, int64_t count, const void* params, int dtype, void* stream);
+
+/* x <- tanh(x) in place (T). */
+B200H_API int b200h_tanh(void* x, int64_t count, int dtype, void* stream);
+
+/* Router with sigmoid scores s and groups of neighbouring experts: choice score = s + correction (float [experts] or NULL); a
+ * group's score = the sum of its group_top largest choice scores; only experts of the `keep` best of `groups` equal groups can be
+ * chosen; ids = the `top` largest choice scores; wts = the chosen s (without correction), / (their sum + 1e-20) if renorm, * scale. */
+B200H_API int b200h_route_grouped(const void* x, int x_dtype, const void* router, const void* correction, int n, int width, int experts,
+                                  int top, int groups, int keep, int group_top, int renorm, float scale, void* ids, void* wts, void* stream);
+
 #endif
 
 #define B200H_BF16 1
@@ -198,10 +250,17 @@ typedef struct b200h_window_args {
     int dtype;
     void* stream;
     const void* sink;        /* float [heads] or NULL */
+    int chunk;               /* > 0: a query sees only keys j with j / chunk == i / chunk (chunks counted from position 0) */
+    int talk_scores;         /* 1: talk mixes the heads' SCORES before the softmax (s_h <- sum_g talk[h, g] * s_g) instead of their weights */
+    int gate_heads;          /* 1: gate is T [n, ld_gate] with ONE column per head instead of one per output column */
 } b200h_window_args;
 /* Bias, norm of query and key, cache store of key and value (fills qn). */
 B200H_API int b200h_window_prep(const b200h_window_args* args);
-/* Attention of the step's rows over the cache (fills y); the step's own rows must have been stored by b200h_window_prep. */
+/* The same for an attention that norms PER HEAD and rotates: bias, then every head of q and k divided by its root mean square over
+ * dim and multiplied by q_norm / k_norm (float [dim], shared by all heads; NULL: no norm), then the rotation rot of every head; cache
+ * store of key and (biased) value (fills qn). */
+B200H_API int b200h_head_rope_prep(const b200h_window_args* args, const b200h_rotary* rot);
+/* Attention of the step's rows over the cache (fills y); the step's own rows must have been stored by a prep entry. */
 B200H_API int b200h_window_attention(const b200h_window_args* args);
 
 /* ---- parallel blocks (both sublayers read the same stream), convolved rotary attention, state-space mixer ---- */
@@ -264,5 +323,55 @@ B200H_API int b200h_softcap(void* x, int64_t count, float cap, void* stream);
 
 /* u[r, :] <- relu(scale[r] * u[r, :])^2 in place (u T [rows, cols], scale float [rows] or NULL). */
 B200H_API int b200h_scaled_relu2(void* u, const void* scale, int rows, int cols, int dtype, void* stream);
+
+
+/* ---- parallel blocks with one norm and a token shift, side-by-side mixers, recurrence with a decay per channel and token ---- */
+
+/* out[t] = table[tokens[t]] + second[row] (float), row = (previous token * mul_prev + tokens[t] * mul_cur) mod buckets, or `buckets`
+ * (the table's last row) at position 0.  The token before an entry's first row is the int at prev + seq_slot[s] * slot_stride (in
+ * a float's place), which then becomes the entry's last token of this step. */
+B200H_API int b200h_embed_hashed(const void* tokens, const void* table, const void* second, int buckets, int mul_prev, int mul_cur, void* prev,
+                                 int64_t slot_stride, const void* tok_seq, const void* tok_pos, const void* cu_q, const void* seq_slot,
+                                 void* out, int n, int batch, int width, int dtype, void* stream);
+
+/* x[t] += branch_scale * (left[t] / rms(left[t]) * wl + right[t] / rms(right[t]) * wr) + sum_p ff[t, p]; then, if w is given,
+ * hf[t] = x[t] / rms(x[t]) * w (float) and h[t] the same as T.  left, right: T [n, width] (both or neither) with wl, wr float
+ * [width]; ff: T (or float when ff_is_f32) [n, parts, width] or NULL; h, hf optional. */
+B200H_API int b200h_branch_residual_norm(void* x, const void* left, const void* right, const void* wl, const void* wr, float branch_scale,
+                                         const void* ff, int ff_is_f32, int parts, const void* w, int n, int width, float eps, void* h,
+                                         void* hf, int dtype, void* stream);
+
+/* Token shift of normed rows h (float [n, width]): a[t] = h[t] + (h[t-1] - h[t]) * shift (shift float [width] or NULL: a = h), and
+ * for m < nmu blends[m][t] = a[t] + (a[t-1] - a[t]) * mu[m] (mu float [nmu, width]; a, blends T, blends [nmu, n, width]; a optional).
+ * The rows before an entry's first come from its state (float [2, width] = its last h and a at state + seq_slot[s] * slot_stride;
+ * zeros at a sequence's start), which is then advanced by the step. */
+B200H_API int b200h_token_shift(const void* h, const void* shift, const void* mu, int nmu, void* state, int64_t slot_stride,
+                                const void* tok_seq, const void* cu_q, const void* seq_slot, int n, int batch, int width, void* a,
+                                void* blends, int dtype, void* stream);
+
+/* Per head, S a [dim, vdim] float matrix per sequence:  w_t = exp(-exp(d_t + w0)) per key channel;
+ * out_t = (S + diag(bonus) k_t v_t^T)^T r_t;  S <- diag(w_t) S + k_t v_t^T.  r, k (heads * dim columns) and v (heads * vdim) are T
+ * with row stride ld; d float [n, heads * dim]; w0, bonus float [heads * dim]; state float [heads, vdim, dim] at state + seq_slot[s] *
+ * slot_stride, read and advanced; decay: float [n, heads * dim] scratch; out float [n, heads * vdim]. */
+B200H_API int b200h_channel_decay_scan(const void* r, const void* k, const void* v, int64_t ld, const void* d, const void* w0,
+                                       const void* bonus, void* state, int64_t slot_stride, const void* cu_q, const void* seq_slot, int n,
+                                       int batch, int heads, int dim, int vdim, void* decay, void* out, int dtype, void* stream);
+
+/* y[t] = unit_rms_per_group(o[t]) * w * act(gate[t]) as T: the norm BEFORE the gate; o float [n, count], `groups` equal parts,
+ * gate T with row stride ld_gate; act 0 sigmoid, 1 silu. */
+B200H_API int b200h_group_norm_gate(const void* o, const void* w, const void* gate, int64_t ld_gate, int n, int count, int groups, int act,
+                                    float eps, void* y, int dtype, void* stream);
+
+/* x <- z > 0 ? softplus(p) z^2 + z / 2 : (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 in place (T); params = {p, q} floats on the device. */
+B200H_API int b200h_xielu(void* x, int64_t count, const void* params, int dtype, void* stream);
+
+/* x <- tanh(x) in place (T). */
+B200H_API int b200h_tanh(void* x, int64_t count, int dtype, void* stream);
+
+/* Router with sigmoid scores s and groups of neighbouring experts: choice score = s + correction (float [experts] or NULL); a
+ * group's score = the sum of its group_top largest choice scores; only experts of the `keep` best of `groups` equal groups can be
+ * chosen; ids = the `top` largest choice scores; wts = the chosen s (without correction), / (their sum + 1e-20) if renorm, * scale. */
+B200H_API int b200h_route_grouped(const void* x, int x_dtype, const void* router, const void* correction, int n, int width, int experts,
+                                  int top, int groups, int keep, int group_top, int renorm, float scale, void* ids, void* wts, void* stream);
 
 #endif

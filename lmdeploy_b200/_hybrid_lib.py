@@ -49,6 +49,7 @@ class WindowArgs(C.Structure):
         ("ml", C.c_void_p), ("o_part", C.c_void_p), ("scores", C.c_void_p), ("score_ld", C.c_int64), ("y", C.c_void_p),
         ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("block_ptrs", C.c_void_p), ("cu_blocks", C.c_void_p),
         ("layer_off", C.c_int64), ("v_off", C.c_int64), ("dtype", C.c_int), ("stream", C.c_void_p), ("sink", C.c_void_p),
+        ("chunk", C.c_int), ("talk_scores", C.c_int), ("gate_heads", C.c_int),
     ]
 
 
@@ -65,6 +66,7 @@ class ConvPrepArgs(C.Structure):
 
 
 SCORE_FN = {"softmax": 0, "sigmoid": 1}
+GATE_ACT = {"sigmoid": 0, "silu": 1}
 EXPERT_ACT = {"silu_gate": 0, "relu2": 1}
 
 _lib = None
@@ -111,6 +113,15 @@ def load():
     lib.b200h_conv_rope_prep.argtypes = [C.POINTER(ConvPrepArgs)]
     lib.b200h_softcap.argtypes = [P, L64, F, P]
     lib.b200h_scaled_relu2.argtypes = [P, P, I, I, I, P]
+    lib.b200h_head_rope_prep.argtypes = [C.POINTER(WindowArgs), C.POINTER(Rotary)]
+    lib.b200h_embed_hashed.argtypes = [P, P, P, I, I, I, P, L64, P, P, P, P, P, I, I, I, I, P]
+    lib.b200h_branch_residual_norm.argtypes = [P, P, P, P, P, F, P, I, I, P, I, I, F, P, P, I, P]
+    lib.b200h_token_shift.argtypes = [P, P, P, I, P, L64, P, P, P, I, I, I, P, P, I, P]
+    lib.b200h_channel_decay_scan.argtypes = [P, P, P, L64, P, P, P, P, L64, P, P, I, I, I, I, I, P, P, I, P]
+    lib.b200h_group_norm_gate.argtypes = [P, P, P, L64, I, I, I, I, F, P, I, P]
+    lib.b200h_xielu.argtypes = [P, L64, P, I, P]
+    lib.b200h_tanh.argtypes = [P, L64, I, P]
+    lib.b200h_route_grouped.argtypes = [P, I, P, P, I, I, I, I, I, I, I, I, F, P, P, P]
     _lib = lib
     return lib
 

@@ -514,6 +514,85 @@ __global__ void route_kernel(const TI* __restrict__ x, const float* __restrict__
     }
 }
 
+// Router with sigmoid scores s = sigmoid(router x) and a choice among GROUPS of neighbouring experts: the choice score of an
+// expert is s + correction (correction nullptr: s); a group's score is the sum of its `group_top` largest choice scores; only the
+// experts of the `keep` best groups can be chosen (ties: the lower index), the `top` with the largest choice scores are.  The
+// weights are the chosen experts' s WITHOUT the correction, divided by their sum + 1e-20 when renorm, times scale.
+// Shared memory: width floats of x, then experts logits, experts choice scores, groups group scores.
+template <typename TI>
+__global__ void route_grouped_kernel(const TI* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
+                                     int width, int experts, int top, int groups, int keep, int group_top, int renorm, float scale,
+                                     int* __restrict__ ids, float* __restrict__ wts)
+{
+    extern __shared__ float sm[];
+    float* xs = sm;
+    float* sc = sm + width;
+    float* ch = sc + experts;
+    float* gs = ch + experts;
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(x[(size_t)t * width + i]);
+    __syncthreads();
+    for (int e = warp; e < experts; e += nw) {
+        const float* row = router + (size_t)e * width;
+        float part = 0.f;
+        for (int i = lane; i < width; i += 32) part = fmaf(row[i], xs[i], part);
+        part = warp_sum(part);
+        if (lane == 0) {
+            sc[e] = sigmoid_f(part);
+            ch[e] = sc[e] + (correction ? correction[e] : 0.f);
+        }
+    }
+    __syncthreads();
+    const int per = experts / groups;
+    if (groups > 1 && keep < groups) {
+        // a group's score: its group_top largest choice scores, found by repeated selection (one thread per group)
+        for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+            float total = 0.f, bound = INFINITY;
+            int bound_at = -1;                          // the last one taken: equal values are taken in index order
+            for (int k = 0; k < group_top && k < per; ++k) {
+                float bv = -INFINITY;
+                int best = -1;
+                for (int e = 0; e < per; ++e) {
+                    const float c = ch[g * per + e];
+                    const bool after = c < bound || (c == bound && e > bound_at);
+                    if (after && (best < 0 || c > bv)) { bv = c; best = e; }
+                }
+                total += bv;
+                bound = bv;
+                bound_at = best;
+            }
+            gs[g] = total;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            // groups that are NOT kept: the groups - keep worst (ties: the higher index goes first)
+            for (int k = 0; k < groups - keep; ++k) {
+                int worst = -1;
+                float wv = INFINITY;
+                for (int g = 0; g < groups; ++g)
+                    if (gs[g] == gs[g] && (worst < 0 || gs[g] <= wv)) { wv = gs[g]; worst = g; }
+                gs[worst] = nanf("");
+                for (int e = 0; e < per; ++e) ch[worst * per + e] = -INFINITY;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int best = -1;
+            float bv = -INFINITY;
+            for (int e = 0; e < experts; ++e)
+                if (ch[e] == ch[e] && (best < 0 || ch[e] > bv)) { bv = ch[e]; best = e; }
+            ids[(size_t)t * top + k] = best;
+            sum += sc[best];
+            ch[best] = nanf("");                        // taken
+        }
+        const float f = (renorm ? 1.0f / (sum + 1e-20f) : 1.0f) * scale;
+        for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] = sc[ids[(size_t)t * top + k]] * f;
+    }
+}
+
 // Experts for a step of few rows, expert-major so that an expert's weights stream from HBM once whatever the number of rows
 // that chose it.  Entry i = (row i / top, choice i % top).  expert_lists_kernel collects every expert's entries;
 // expert_rows_kernel gives a block 32 weight rows of one expert and walks that expert's entries eight at a time: the
@@ -704,6 +783,7 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int 
 #include "window_attention.cuh"
 #include "ssm.cuh"
 #include "parallel_block.cuh"
+#include "token_shift.cuh"
 
 }  // namespace b200h
 
@@ -1061,7 +1141,8 @@ B200H_API int b200h_relu2(void* x, int64_t count, int dtype, void* stream)
 static int window_args_ok(const b200h_window_args* a, const char** why)
 {
     if (!a || !a->tok_seq || !a->tok_pos || !a->block_ptrs || !a->cu_blocks || !a->qn) { *why = "window attention: bad arguments"; return 0; }
-    if (a->heads <= 0 || a->kv_heads <= 0 || a->heads % a->kv_heads || a->dim <= 0 || a->vdim <= 0 || a->block_len <= 0 || a->window < 0) {
+    if (a->heads <= 0 || a->kv_heads <= 0 || a->heads % a->kv_heads || a->dim <= 0 || a->vdim <= 0 || a->block_len <= 0 || a->window < 0 ||
+        a->chunk < 0 || (a->talk_scores && !a->talk)) {
         *why = "window attention: heads must be a multiple of kv_heads, sizes positive";
         return 0;
     }
@@ -1082,12 +1163,33 @@ B200H_API int b200h_window_prep(const b200h_window_args* a)
     return launched("window_prep");
 }
 
+B200H_API int b200h_head_rope_prep(const b200h_window_args* a, const b200h_rotary* r)
+{
+    const char* why = "";
+    if (!window_args_ok(a, &why)) return fail(B200H_ERR_INVALID_ARG, why);
+    if (!a->q || !a->k || !a->v || !r || r->pairs < 0 || 2 * r->pairs > a->dim || (r->pairs && !r->freqs))
+        return fail(B200H_ERR_INVALID_ARG, "head_rope_prep: bad arguments (2 * rot.pairs <= dim)");
+    if (a->n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)a->stream;
+    const Rotary rot = make_rotary(r);
+    const size_t smem = ((size_t)(a->heads + a->kv_heads) * a->dim + 2 * (size_t)rot.pairs) * sizeof(float);
+    if (smem > 200 * 1024) return fail(B200H_ERR_UNSUPPORTED, "head_rope_prep: (heads + kv_heads) * dim floats exceed an SM's shared memory");
+    B200H_DISPATCH_T(a->dtype, {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(head_rope_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        head_rope_prep_kernel<T><<<a->n, 256, smem, st>>>(
+            (const T*)a->q, (const T*)a->k, (const T*)a->v, a->ld, a->heads, a->kv_heads, a->dim, a->vdim, (const float*)a->bias,
+            (const float*)a->q_norm, (const float*)a->k_norm, a->eps, rot, (const int*)a->tok_seq, (const int*)a->tok_pos,
+            (const int64_t*)a->block_ptrs, (const int*)a->cu_blocks, a->layer_off, a->v_off, a->block_len, (float*)a->qn);
+    });
+    return launched("head_rope_prep");
+}
+
 static size_t window_pv_smem(const b200h_window_args* a, int rows, int tile)
 {
     const size_t H = a->heads, rh = (size_t)rows * H;
     auto pad4 = [](size_t v) { return (v + 3) & ~(size_t)3; };
-    return (size_t)tile * sizeof(char*) +
-           sizeof(float) * (2 * pad4(rh) + (a->talk ? pad4(H * H) : 0) + (size_t)(a->talk ? 2 : 1) * rh * tile + rh * a->vdim);
+    const bool talk = a->talk && !a->talk_scores;           // pass 2 recombines weights only when the scores were not mixed before it
+    return (size_t)tile * sizeof(char*) + sizeof(float) * (2 * pad4(rh) + (talk ? pad4(H * H) : 0) + (size_t)(talk ? 2 : 1) * rh * tile + rh * a->vdim);
 }
 
 struct WindowLaunch {
@@ -1104,6 +1206,15 @@ static void launch_window_kernels(const b200h_window_args* a, const WindowGeom& 
         cudaFuncSetAttribute(window_pv_kernel<T, CW, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)l.pv_smem);
     window_stats_kernel<T, VEC, NP><<<dim3(l.blocks, a->kv_heads, a->splits), l.stats_threads, l.stats_smem, st>>>((const float*)a->qn, g,
                                                                                                                    (float*)a->ml);
+    if (a->talk_scores) {
+        // between the passes: the scores of all heads of a row are mixed in place and their maxima and denominators recomputed
+        const int H = a->heads;
+        int tile = 128;
+        while (tile > 8 && (size_t)H * (H + tile) * sizeof(float) > 96 * 1024) tile /= 2;
+        const size_t smem = (size_t)H * (H + tile) * sizeof(float);
+        if (smem > 48 * 1024) cudaFuncSetAttribute(window_mix_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        window_mix_scores_kernel<<<a->n, 256, smem, st>>>(g, (const float*)a->talk, tile, (float*)a->ml);
+    }
     window_pv_kernel<T, CW, NP><<<dim3(l.blocks, a->splits), 256, l.pv_smem, st>>>(g, (const float*)a->ml, (float*)a->o_part);
 }
 
@@ -1120,7 +1231,8 @@ static int launch_window_attention(const b200h_window_args* a, WindowGeom g, cud
     while (window_pv_smem(a, g.rows, g.tile) > budget && g.rows > 1) g.rows /= 2;
     WindowLaunch l;
     // pass 1: a thread per key of the range, at most 128
-    const int keys = a->window > 0 ? a->window + g.rows - 1 : 1 << 30, per = (keys + a->splits - 1) / a->splits;
+    const int span = a->window > 0 && a->chunk > 0 ? (a->window < a->chunk ? a->window : a->chunk) : (a->window > 0 ? a->window : a->chunk);
+    const int keys = span > 0 ? span + g.rows - 1 : 1 << 30, per = (keys + a->splits - 1) / a->splits;
     l.stats_threads = per <= 32 ? 32 : (per <= 64 ? 64 : 128);
     l.stats_smem = (size_t)g.rows * rep * a->dim * sizeof(float) + (VEC ? (size_t)l.stats_threads * (a->dim * sizeof(T) + 16) : 0);
     l.pv_smem = window_pv_smem(a, g.rows, g.tile);
@@ -1132,7 +1244,7 @@ static int launch_window_attention(const b200h_window_args* a, WindowGeom g, cud
     else if (pairs <= 4) launch_window_kernels<T, VEC, CW, 4>(a, g, l, st);
     else launch_window_kernels<T, VEC, CW, 8>(a, g, l, st);
     window_out_kernel<T><<<dim3(a->n, (H * a->vdim + 255) / 256), 256, 0, st>>>((const float*)a->o_part, a->splits, H * a->vdim, (const T*)a->gate,
-                                                                                a->ld_gate, (T*)a->y);
+                                                                                a->ld_gate, a->gate_heads ? a->vdim : 1, (T*)a->y);
     return 0;
 }
 
@@ -1147,8 +1259,10 @@ B200H_API int b200h_window_attention(const b200h_window_args* a)
     WindowGeom g;
     g.n = a->n; g.rows = 1; g.tile = 32;
     g.heads = a->heads; g.kv_heads = a->kv_heads; g.dim = a->dim; g.vdim = a->vdim; g.block_len = a->block_len;
-    g.window = a->window; g.splits = a->splits; g.scale = a->scale; g.softcap = a->softcap;
-    g.r1 = (const float*)a->r1; g.r2 = (const float*)a->r2; g.talk = (const float*)a->talk; g.sink = (const float*)a->sink;
+    g.window = a->window; g.splits = a->splits; g.scale = a->scale; g.softcap = a->softcap; g.chunk = a->chunk;
+    // talk mixes the softmax WEIGHTS inside pass 2, or (talk_scores) the SCORES between the passes: pass 2 then sees no talk
+    g.r1 = (const float*)a->r1; g.r2 = (const float*)a->r2; g.talk = a->talk_scores ? nullptr : (const float*)a->talk;
+    g.sink = (const float*)a->sink;
     g.tok_seq = (const int*)a->tok_seq; g.tok_pos = (const int*)a->tok_pos;
     g.block_ptrs = (const int64_t*)a->block_ptrs; g.cu_blocks = (const int*)a->cu_blocks;
     g.layer_off = a->layer_off; g.v_off = a->v_off;
@@ -1287,4 +1401,141 @@ B200H_API int b200h_scaled_relu2(void* u, const void* scale, int rows, int cols,
     const int64_t count = (int64_t)rows * cols;
     B200H_DISPATCH_T(dtype, scaled_relu2_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, st>>>((T*)u, (const float*)scale, cols, count));
     return launched("scaled_relu2");
+}
+
+// ------------------------------------------------------------------------------------------------ one-norm parallel blocks, token shift
+B200H_API int b200h_embed_hashed(const void* tokens, const void* table, const void* second, int buckets, int mul_prev, int mul_cur, void* prev,
+                                 int64_t slot_stride, const void* tok_seq, const void* tok_pos, const void* cu_q, const void* seq_slot,
+                                 void* out, int n, int batch, int width, int dtype, void* stream)
+{
+    if (!tokens || !table || !second || !prev || !tok_seq || !tok_pos || !cu_q || !seq_slot || !out || n < 0 || batch <= 0 || width <= 0 ||
+        buckets <= 0)
+        return fail(B200H_ERR_INVALID_ARG, "embed_hashed: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, embed_hashed_kernel<T><<<n, 256, 0, st>>>((const int*)tokens, (const T*)table, (const T*)second, buckets, mul_prev,
+                                                                     mul_cur, (const float*)prev, slot_stride, (const int*)tok_seq,
+                                                                     (const int*)tok_pos, (const int*)cu_q, (const int*)seq_slot, (float*)out,
+                                                                     width));
+    last_token_kernel<<<(batch + 127) / 128, 128, 0, st>>>((const int*)tokens, (float*)prev, slot_stride, (const int*)cu_q, (const int*)seq_slot,
+                                                         batch);
+    return launched("embed_hashed");
+}
+
+B200H_API int b200h_branch_residual_norm(void* x, const void* left, const void* right, const void* wl, const void* wr, float branch_scale,
+                                         const void* ff, int ff_is_f32, int parts, const void* w, int n, int width, float eps, void* h,
+                                         void* hf, int dtype, void* stream)
+{
+    if (!x || n < 0 || width <= 0 || (!left != !right) || (left && (!wl || !wr)) || (ff && parts < 1) || ((h || hf) && !w))
+        return fail(B200H_ERR_INVALID_ARG, "branch_residual_norm: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+#define B200H_JOIN(TF)                                                                                                                     \
+    branch_residual_norm_kernel<T, TF><<<n, 256, 0, st>>>((float*)x, (const T*)left, (const T*)right, (const float*)wl, (const float*)wr,   \
+                                                          branch_scale, (const TF*)ff, ff ? parts : 0, (const float*)w, width, eps, (T*)h,  \
+                                                          (float*)hf)
+    B200H_DISPATCH_T(dtype, if (ff_is_f32) B200H_JOIN(float); else B200H_JOIN(T));
+#undef B200H_JOIN
+    return launched("branch_residual_norm");
+}
+
+B200H_API int b200h_token_shift(const void* h, const void* shift, const void* mu, int nmu, void* state, int64_t slot_stride,
+                                const void* tok_seq, const void* cu_q, const void* seq_slot, int n, int batch, int width, void* a,
+                                void* blends, int dtype, void* stream)
+{
+    if (!h || !state || !tok_seq || !cu_q || !seq_slot || n < 0 || batch <= 0 || width <= 0 || nmu < 0 || (nmu && (!mu || !blends)))
+        return fail(B200H_ERR_INVALID_ARG, "token_shift: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, token_shift_kernel<T><<<n, 256, 0, st>>>((const float*)h, (const float*)shift, (const float*)mu, nmu,
+                                                                    (const float*)state, slot_stride, (const int*)tok_seq, (const int*)cu_q,
+                                                                    (const int*)seq_slot, n, width, (T*)a, (T*)blends));
+    token_shift_state_kernel<<<dim3((width + 255) / 256, batch), 256, 0, st>>>((const float*)h, (const float*)shift, (float*)state, slot_stride,
+                                                                             (const int*)cu_q, (const int*)seq_slot, width);
+    return launched("token_shift");
+}
+
+B200H_API int b200h_channel_decay_scan(const void* r, const void* k, const void* v, int64_t ld, const void* d, const void* w0,
+                                       const void* bonus, void* state, int64_t slot_stride, const void* cu_q, const void* seq_slot, int n,
+                                       int batch, int heads, int dim, int vdim, void* decay, void* out, int dtype, void* stream)
+{
+    if (!r || !k || !v || !d || !w0 || !bonus || !state || !cu_q || !seq_slot || !decay || !out || n < 0 || batch <= 0 || heads <= 0 ||
+        dim <= 0 || vdim <= 0)
+        return fail(B200H_ERR_INVALID_ARG, "channel_decay_scan: bad arguments");
+    if (dim > 256) return fail(B200H_ERR_UNSUPPORTED, "channel_decay_scan: dim <= 256");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t count = (int64_t)n * heads * dim;
+    channel_decay_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>((const float*)d, (const float*)w0, heads * dim, count, (float*)decay);
+    // two value columns per warp where the head has an even number of them (r, k and the decays are read once for both)
+    const int nc = vdim % 2 == 0 ? 2 : 1, units = vdim / nc, warps = units < 8 ? units : 8;
+    const dim3 grid((units + warps - 1) / warps, heads, batch), block(32, warps);
+    const int nw = (dim + 31) / 32;
+#define B200H_SCAN(NW, NC)                                                                                                                  \
+    channel_decay_scan_kernel<T, NW, NC><<<grid, block, 0, st>>>((const T*)r, (const T*)k, (const T*)v, ld, (const float*)decay,              \
+                                                                 (const float*)bonus, (float*)state, slot_stride, (const int*)cu_q,          \
+                                                                 (const int*)seq_slot, heads, dim, vdim, (float*)out)
+#define B200H_SCAN_NW(NC) \
+    do { if (nw <= 1) B200H_SCAN(1, NC); else if (nw <= 2) B200H_SCAN(2, NC); else if (nw <= 4) B200H_SCAN(4, NC); else B200H_SCAN(8, NC); } while (0)
+    B200H_DISPATCH_T(dtype, if (nc == 2) B200H_SCAN_NW(2); else B200H_SCAN_NW(1));
+#undef B200H_SCAN_NW
+#undef B200H_SCAN
+    return launched("channel_decay_scan");
+}
+
+B200H_API int b200h_group_norm_gate(const void* o, const void* w, const void* gate, int64_t ld_gate, int n, int count, int groups, int act,
+                                    float eps, void* y, int dtype, void* stream)
+{
+    if (!o || !w || !gate || !y || count <= 0 || groups <= 0 || count % groups || act < 0 || act > 1)
+        return fail(B200H_ERR_INVALID_ARG, "group_norm_gate: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, group_norm_gate_kernel<T><<<dim3(n, groups), 128, 0, st>>>((const float*)o, (const float*)w, (const T*)gate, ld_gate,
+                                                                                      count, groups, act, eps, (T*)y));
+    return launched("group_norm_gate");
+}
+
+B200H_API int b200h_xielu(void* x, int64_t count, const void* params, int dtype, void* stream)
+{
+    if (!x || !params || count < 0) return fail(B200H_ERR_INVALID_ARG, "xielu: bad arguments");
+    if (count == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, xielu_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, st>>>((T*)x, count, (const float*)params));
+    return launched("xielu");
+}
+
+B200H_API int b200h_tanh(void* x, int64_t count, int dtype, void* stream)
+{
+    if (!x || count < 0) return fail(B200H_ERR_INVALID_ARG, "tanh: bad arguments");
+    if (count == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, tanh_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, st>>>((T*)x, count));
+    return launched("tanh");
+}
+
+template <typename TI>
+static void launch_route_grouped(const void* x, const void* router, const void* correction, int n, int width, int experts, int top, int groups,
+                                 int keep, int group_top, int renorm, float scale, void* ids, void* wts, size_t smem, cudaStream_t st)
+{
+    if (smem > 48 * 1024) cudaFuncSetAttribute(route_grouped_kernel<TI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    route_grouped_kernel<TI><<<n, 256, smem, st>>>((const TI*)x, (const float*)router, (const float*)correction, width, experts, top, groups, keep,
+                                                  group_top, renorm, scale, (int*)ids, (float*)wts);
+}
+
+B200H_API int b200h_route_grouped(const void* x, int x_dtype, const void* router, const void* correction, int n, int width, int experts,
+                                  int top, int groups, int keep, int group_top, int renorm, float scale, void* ids, void* wts, void* stream)
+{
+    if (!x || !router || !ids || !wts || experts <= 0 || top <= 0 || groups <= 0 || experts % groups || keep < 1 || keep > groups ||
+        group_top < 1 || top > keep * (experts / groups))
+        return fail(B200H_ERR_INVALID_ARG, "route_grouped: bad arguments (equal groups, top within the kept groups)");
+    if (n == 0) return 0;
+    const size_t smem = (size_t)(width + 2 * experts + groups) * sizeof(float);
+    if (smem > 200 * 1024) return fail(B200H_ERR_UNSUPPORTED, "route_grouped: width + experts exceeds shared memory");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dtype == B200H_F32)
+        launch_route_grouped<float>(x, router, correction, n, width, experts, top, groups, keep, group_top, renorm, scale, ids, wts, smem, st);
+    else if (x_dtype == B200H_BF16)
+        launch_route_grouped<bf16>(x, router, correction, n, width, experts, top, groups, keep, group_top, renorm, scale, ids, wts, smem, st);
+    else return fail(B200H_ERR_UNSUPPORTED, "dtype: float32 (2) or bfloat16 (1)");
+    return launched("route_grouped");
 }

@@ -110,6 +110,7 @@ __global__ void window_prep_kernel(const T* __restrict__ q, const T* __restrict_
 
 struct WindowGeom {
     int n, heads, kv_heads, dim, vdim, block_len, window, splits;
+    int chunk;                // > 0: a row sees only the keys of its own chunk of this many positions, counted from position 0
     int rows;                 // rows of the step per block (consecutive rows; a block walks the keys once for those of one sequence)
     int tile;                 // keys per tile of pass 2, a multiple of 4, at most 256
     float scale, softcap;
@@ -127,13 +128,17 @@ struct WindowGeom {
 };
 
 // first visible key of a row at position pos
-__device__ __forceinline__ int window_first(const WindowGeom& g, int pos) { return g.window > 0 ? max(0, pos - g.window + 1) : 0; }
+__device__ __forceinline__ int window_first(const WindowGeom& g, int pos)
+{
+    const int lo = g.window > 0 ? max(0, pos - g.window + 1) : 0;
+    return g.chunk > 0 ? max(lo, pos / g.chunk * g.chunk) : lo;
+}
 
 // The key range `z` of consecutive rows of one sequence at positions first .. last: [j0, j1).  Every row masks the keys of the
 // range that it does not see.
 __device__ __forceinline__ void window_range(const WindowGeom& g, int first, int last, int z, int& j0, int& j1)
 {
-    const int lo = g.window > 0 ? max(0, first - g.window + 1) : 0;
+    const int lo = window_first(g, first);
     const int per = (last - lo + g.splits) / g.splits;         // ceil((last - lo + 1) / splits)
     j0 = lo + z * per;
     j1 = min(last + 1, j0 + per);
@@ -141,7 +146,7 @@ __device__ __forceinline__ void window_range(const WindowGeom& g, int first, int
 
 __device__ __forceinline__ bool window_sees(const WindowGeom& g, int pos, int j)
 {
-    return j <= pos && (g.window == 0 || j > pos - g.window);
+    return j <= pos && j >= window_first(g, pos);
 }
 
 // score of head `head` for a key at distance `dist` behind the query, from the raw dot product
@@ -444,10 +449,10 @@ __global__ void __launch_bounds__(256) window_pv_kernel(WindowGeom g, const floa
     }
 }
 
-// y[t, i] = (sum over ranges of o_part[t, z, i]) * sigmoid(gate[t, i]) as T
+// y[t, i] = (sum over ranges of o_part[t, z, i]) * sigmoid(gate[t, i / gate_div]) as T (gate_div 1: a gate per column; vdim: one per head)
 template <typename T>
 __global__ void window_out_kernel(const float* __restrict__ o_part, int splits, int cols, const T* __restrict__ gate, int64_t ld_gate,
-                                  T* __restrict__ y)
+                                  int gate_div, T* __restrict__ y)
 {
     const int t = blockIdx.x, i = blockIdx.y * blockDim.x + threadIdx.x;          // one column per thread
     if (i >= cols) return;
@@ -455,6 +460,117 @@ __global__ void window_out_kernel(const float* __restrict__ o_part, int splits, 
     float a = 0.f;
 #pragma unroll 8
     for (int z = 0; z < splits; ++z) a += src[(size_t)z * cols];
-    if (gate) a *= sigmoid_f(to_f(gate[(size_t)t * ld_gate + i]));
+    if (gate) a *= sigmoid_f(to_f(gate[(size_t)t * ld_gate + i / gate_div]));
     y[(size_t)t * cols + i] = from_f<T>(a);
+}
+
+// Scores mixed ACROSS heads before the softmax: for every row and visible key, s'_h = sum_g talk[h, g] s_g, in place in the
+// scratch pass 1 left, then every (row, head)'s running maximum and denominator over the mixed scores (into key range 0; the
+// other ranges get the neutral pair, pass 2 merges them all).  One block per row; a tile of keys of all heads passes through
+// shared memory: talk [heads][heads] | tile [heads][keys] floats.
+__global__ void __launch_bounds__(256) window_mix_scores_kernel(WindowGeom g, const float* __restrict__ talk, int tile, float* __restrict__ ml)
+{
+    extern __shared__ __align__(16) float mix_smem[];
+    const int t = blockIdx.x, H = g.heads, tid = threadIdx.x, nt = blockDim.x;
+    const int pos = g.tok_pos[t], keys = pos - window_first(g, pos) + 1;
+    float* tk = mix_smem;
+    float* raw = mix_smem + H * H;
+    float* row = g.scores + (size_t)t * H * g.score_ld;
+    for (int i = tid; i < H * H; i += nt) tk[i] = talk[i];
+    for (int j0 = 0; j0 < keys; j0 += tile) {
+        const int kt = min(tile, keys - j0);
+        __syncthreads();
+        for (int i = tid; i < H * kt; i += nt) { const int h = i / kt, jj = i - h * kt; raw[h * tile + jj] = row[(size_t)h * g.score_ld + j0 + jj]; }
+        __syncthreads();
+        for (int i = tid; i < H * kt; i += nt) {
+            const int h = i / kt, jj = i - h * kt;
+            float a = 0.f;
+            for (int k = 0; k < H; ++k) a = fmaf(tk[h * H + k], raw[k * tile + jj], a);
+            row[(size_t)h * g.score_ld + j0 + jj] = a;
+        }
+    }
+    __syncthreads();
+    const int lane = tid & 31, warp = tid >> 5, nw = nt >> 5;
+    for (int h = warp; h < H; h += nw) {
+        float m = -1e30f, l = 0.f;
+        for (int j = lane; j < keys; j += 32) merge_ml(m, l, row[(size_t)h * g.score_ld + j], 1.0f);
+        for (int o = 16; o > 0; o >>= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, m, o), ol = __shfl_xor_sync(0xffffffffu, l, o);
+            merge_ml(m, l, om, ol);
+        }
+        float* dst = ml + ((size_t)t * H + h) * g.splits * 2;
+        for (int z = lane; z < g.splits; z += 32) {
+            dst[2 * z] = z == 0 ? m : -1e30f;
+            dst[2 * z + 1] = z == 0 ? l : 0.f;
+        }
+    }
+}
+
+// One block per row, for an attention whose query and key are normed PER HEAD and then rotated:
+//   1. the projections' biases are added (float);
+//   2. every head of q and of k is divided by its root mean square over `dim` and multiplied by a weight of `dim` entries that all
+//      heads share (wq / wk; nullptr: no norm of that projection);
+//   3. pairs (2i, 2i+1), i < rot.pairs, of every head turn by position * freqs[i];
+//   4. queries -> qn (float), keys and (biased) values -> the row's cache entry as T.
+// Shared memory: (heads + kv_heads) * dim floats, then 2 * rot.pairs floats of cos / sin.
+template <typename T>
+__global__ void head_rope_prep_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int64_t ld, int heads,
+                                      int kv_heads, int dim, int vdim, const float* __restrict__ bias, const float* __restrict__ wq,
+                                      const float* __restrict__ wk, float eps, Rotary rot, const int* __restrict__ tok_seq,
+                                      const int* __restrict__ tok_pos, const int64_t* __restrict__ block_ptrs,
+                                      const int* __restrict__ cu_blocks, int64_t layer_off, int64_t v_off, int block_len,
+                                      float* __restrict__ qn)
+{
+    extern __shared__ __align__(16) float hr_smem[];
+    const int t = blockIdx.x, s = tok_seq[t], pos = tok_pos[t];
+    const int HD = heads * dim, GD = kv_heads * dim, GV = kv_heads * vdim;
+    float* buf = hr_smem;
+    float* cs = hr_smem + HD + GD;
+    float* sn = cs + rot.pairs;
+    for (int i = threadIdx.x; i < rot.pairs; i += blockDim.x) {
+        double sv, cv;
+        sincos((double)pos * rot.freqs[i], &sv, &cv);
+        cs[i] = (float)cv * rot.magnitude;
+        sn[i] = (float)sv * rot.magnitude;
+    }
+    for (int i = threadIdx.x; i < HD + GD; i += blockDim.x) {
+        const float a = i < HD ? to_f(q[(size_t)t * ld + i]) : to_f(k[(size_t)t * ld + i - HD]);
+        buf[i] = a + (bias ? bias[i] : 0.f);
+    }
+    __syncthreads();
+    char* page = reinterpret_cast<char*>(block_ptrs[cu_blocks[s] + pos / block_len]) + layer_off;
+    const int at = pos % block_len;
+    T* k_dst = reinterpret_cast<T*>(page) + (size_t)at * GD;
+    T* v_dst = reinterpret_cast<T*>(page + v_off) + (size_t)at * GV;
+    for (int i = threadIdx.x; i < GV; i += blockDim.x) v_dst[i] = from_f<T>(to_f(v[(size_t)t * ld + i]) + (bias ? bias[HD + GD + i] : 0.f));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int h = warp; h < heads + kv_heads; h += nw) {
+        float* x = buf + (size_t)h * dim;
+        const float* wn = h < heads ? wq : wk;
+        if (wn) {
+            float ss = 0.f;
+            for (int d = lane; d < dim; d += 32) ss += x[d] * x[d];
+            ss = warp_sum(ss);
+            const float r = 1.0f / sqrtf(ss / (float)dim + eps);
+            for (int d = lane; d < dim; d += 32) x[d] = x[d] * r * wn[d];
+        }
+        __syncwarp();
+        // one lane per pair of dimensions; a turning pair is whole (2 * rot.pairs <= dim), the rest pass unchanged
+        for (int d = 2 * lane; d < dim; d += 64) {
+            const bool two = d + 1 < dim;
+            float a = x[d], b = two ? x[d + 1] : 0.f;
+            if (d / 2 < rot.pairs) {
+                const float ra = a * cs[d / 2] - b * sn[d / 2], rb = b * cs[d / 2] + a * sn[d / 2];
+                a = ra;
+                b = rb;
+            }
+            if (h < heads) {
+                qn[(size_t)t * HD + (size_t)h * dim + d] = a;
+                if (two) qn[(size_t)t * HD + (size_t)h * dim + d + 1] = b;
+            } else {
+                k_dst[(size_t)(h - heads) * dim + d] = from_f<T>(a);
+                if (two) k_dst[(size_t)(h - heads) * dim + d + 1] = from_f<T>(b);
+            }
+        }
+    }
 }

@@ -3,11 +3,12 @@
 A hybrid decoder mixes layer kinds, so a sequence owns two things between steps:
   * pages of the engine's block pool (runtime.KvCachePool, handed out by scheduler.BlockAllocator) -- every latent-attention
     layer keeps, per position, its normed key/value latent (as T) and the rotated key part all heads share (as float); every
-    windowed-attention or convolved-rotary-attention layer its normed keys and its values (as T);
+    windowed-, chunked- or convolved-rotary-attention layer its normed (and rotated) keys and its values (as T);
   * one slot of the StatePool (handed out by scheduler.Scheduler's slot list) -- per layer the last taps-1 inputs of the
     short convolution (of both sublayers in pre-norm blocks; of the stacked q | k projection of a convolved attention; of the
-    x | B | C channels of a state-space mixer), per decayed-linear-attention layer the [heads, vdim, dim] float state and per
-    state-space layer the [heads, vdim, state] float state.
+    x | B | C channels of a state-space mixer), per decayed-linear-attention or channel-decay layer the [heads, vdim, dim] float
+    state and per state-space layer the [heads, vdim, state] float state; in shared-norm blocks per run the last normed row and the
+    last shifted row (the token shift), and once the id of the last token (hashed bigram embedding).
 A layer that a spec loops (HybridSpec.loop) is executed several times per step with the same weights: caches and states
 belong to RUNS (HybridSpec.runs()), weights to layers.
 The step is a mixed step like b200_model_chunk_step: any number of rows per sequence, prompt portions beside single decoded
@@ -79,17 +80,25 @@ class HybridModel:
         # cache page: the attention runs' regions one after another; a latent region is [block_len, kv_rank] T then [block_len, rot_dim] float
         # state slot: per run [taps-1, width] conv inputs (twice where the feed-forward has a conv too), then per decay layer [heads, vdim, dim]
         self.cache_off, self.rot_off, self.conv_off, self.mix_off, self.conv2_off, self.v_off = {}, {}, {}, {}, {}, {}
+        self.shift_off = {}
         self.runs = spec.runs()
-        if spec.block not in ("post_norm", "pre_norm", "parallel"):
+        if spec.block not in ("post_norm", "pre_norm", "parallel", "shared_norm"):
             raise NotImplementedError(f"block {spec.block!r}")
         pre = spec.block == "pre_norm"
         page = slot = 0
         taps = spec.conv_taps
+        self.token_off = None
+        if spec.bigram is not None:             # the sequence's last token id, an int in a float's place
+            self.token_off = slot
+            slot += 1
         for r, (i, _) in enumerate(self.runs):
             layer = spec.layers[i]
             m = layer.mixer
             self.conv_off[r] = slot             # parallel blocks have no convolution on the stream: the mixers bring their own
-            if spec.block != "parallel":
+            if spec.block == "shared_norm":     # token shift: the last normed row and the last shifted row
+                self.shift_off[r] = slot
+                slot += 2 * spec.width
+            elif spec.block != "parallel":
                 slot += (taps - 1) * spec.width
             if pre and layer.mlp is not None:
                 self.conv2_off[r] = slot
@@ -125,7 +134,17 @@ class HybridModel:
                     raise NotImplementedError("decayed linear attention: dim <= 256")
                 self.mix_off[r] = slot
                 slot += m.heads * m.vdim * m.dim
-            elif m.kind == "window_attention":
+            elif m.kind in ("window_attention", "paired"):
+                if m.kind == "paired":
+                    if spec.block != "shared_norm" or m.left.kind != "window_attention" or m.right.kind != "channel_decay":
+                        raise NotImplementedError("paired mixers: windowed attention beside a channel-decay recurrence in shared-norm blocks")
+                    if m.right.dim > 256:
+                        raise NotImplementedError("channel-decay recurrence: dim <= 256")
+                    self.mix_off[r] = slot
+                    slot += m.right.heads * m.right.vdim * m.right.dim
+                    m = m.left
+                if m.window and m.chunk:
+                    raise NotImplementedError("windowed attention: a sliding window or chunks, not both")
                 # in a region [block_len, kv_heads * dim] keys as T then [block_len, kv_heads * vdim] values as T
                 self.cache_off[r] = page
                 self.v_off[r] = _align(block_len * m.kv_heads * m.dim * esize)
@@ -184,11 +203,37 @@ class HybridModel:
         def norm_w(name):
             # pre-norm and parallel blocks store a norm weight as its deviation from one: the kernels get the full factor
             t = f32(name, (W,))
-            return t + 1.0 if pre or par else t
+            return t + 1.0 if (pre or par) and not s.plain_norms else t
+
+        def window_weights(p, ck, m):
+            """Windowed attention: checkpoint tensors ck + 'q' ... -> w[p + 'in'] ..."""
+            HD, GD, GV, HV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
+            gate_cols = (m.heads if m.gate_per_head else HV) if m.gate else 0
+            parts = [ck + "q", ck + "k", ck + "v"] + ([ck + "g"] if m.gate else [])
+            w[p + "in"] = lin(*parts, shape=(HD + GD + GV + gate_cols, W))
+            if m.bias:          # added in float by the kernel that norms q and k and stores the cache (no bias pass over the GEMM's output)
+                w[p + "in.b"] = torch.cat([f32(ck + f"{k}.b", (cols,)) for k, cols in (("q", HD), ("k", GD), ("v", GV))]).contiguous()
+            w[p + "o"] = lin(ck + "o", shape=(W, HV))
+            if m.qk_norm:
+                w[p + "q.norm"] = f32(ck + "q.norm", (m.dim,) if m.head_norm else (HD,))
+                w[p + "k.norm"] = f32(ck + "k.norm", (m.dim,) if m.head_norm else (GD,))
+            if m.distance_bias:
+                w[p + "r1"] = f32(ck + "r1", (m.heads,))
+                w[p + "r2"] = f32(ck + "r2", (m.heads,))
+            if m.talking_heads:
+                w[p + "talk"] = f32(ck + "talk", (m.heads, m.heads))
+            if m.sink:
+                w[p + "sink"] = f32(ck + "sink", (m.heads,))
+            if m.rot is not None:
+                freqs, mag = m.rot.frequencies()
+                w[p + "freqs"] = torch.tensor(freqs, dtype=torch.float64, device=dev)
+                w[p + "mag"] = float(mag)
 
         w["embed"] = lin("embed", shape=(s.vocab, W))
         w["head"] = w["embed"] if s.tied_head else lin("head", shape=(s.vocab, W))
         w["final.norm"] = norm_w("final.norm")
+        if s.bigram is not None:
+            w["bigram"] = lin("bigram", shape=(s.bigram.buckets + 1, W))
         if s.max_positions:
             w["pos"] = lin("pos", shape=(s.max_positions, W))
         if s.loop is not None:
@@ -196,7 +241,10 @@ class HybridModel:
         for i, layer in enumerate(s.layers):
             p, m = f"l{i}.", layer.mixer
             w[p + "norm1"] = norm_w(p + "norm1")
-            if not par:
+            shared = s.block == "shared_norm"
+            if shared:
+                w[p + "shift"] = f32(p + "shift", (W,))
+            elif not par:
                 w[p + "canon1"] = f32(p + "canon1", (W, s.conv_taps))
             if s.block == "post_norm":
                 w[p + "dwa"] = f32(p + "dwa", (i + 2,))
@@ -232,20 +280,22 @@ class HybridModel:
                 w[p + "freqs"] = torch.tensor(freqs, dtype=torch.float64, device=dev)
                 w[p + "mag"] = float(mag)
             elif m.kind == "window_attention":
-                HD, GD, GV, HV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
-                parts = [p + "mix.q", p + "mix.k", p + "mix.v"] + ([p + "mix.g"] if m.gate else [])
-                w[p + "in"] = lin(*parts, shape=(HD + GD + GV + (HV if m.gate else 0), W))
-                if m.bias:          # added in float by the kernel that norms q and k and stores the cache (no bias pass over the GEMM's output)
-                    w[p + "in.b"] = torch.cat([f32(p + f"mix.{k}.b", (cols,)) for k, cols in (("q", HD), ("k", GD), ("v", GV))]).contiguous()
-                w[p + "o"] = lin(p + "mix.o", shape=(W, HV))
-                if m.qk_norm:
-                    w[p + "q.norm"] = f32(p + "mix.q.norm", (HD,))
-                    w[p + "k.norm"] = f32(p + "mix.k.norm", (GD,))
-                if m.distance_bias:
-                    w[p + "r1"] = f32(p + "mix.r1", (m.heads,))
-                    w[p + "r2"] = f32(p + "mix.r2", (m.heads,))
-                if m.talking_heads:
-                    w[p + "talk"] = f32(p + "mix.talk", (m.heads, m.heads))
+                window_weights(p, p + "mix.", m)
+            elif m.kind == "paired":
+                window_weights(p + "left.", p + "mix.left.", m.left)
+                R, ck = m.right, p + "mix.right."
+                HD = R.heads * R.dim
+                # r | k | v | g stacked for ONE batched product over the four blends; the decay's two matrices apart
+                w[p + "right.in"] = torch.stack([lin(ck + k, shape=(HD, W)) for k in "rkvg"]).contiguous()
+                w[p + "right.mu"] = torch.stack([f32(ck + "mu." + k, (W,)) for k in "rkvgw"]).contiguous()
+                w[p + "right.w1"] = lin(ck + "w1", shape=(R.rank, W))
+                w[p + "right.w2"] = lin(ck + "w2", shape=(HD, R.rank))
+                w[p + "right.w0"] = f32(ck + "w0", (HD,))
+                w[p + "right.u"] = f32(ck + "u", (R.heads, R.dim))
+                w[p + "right.norm"] = f32(ck + "norm", (HD,))
+                w[p + "right.o"] = lin(ck + "o", shape=(W, HD))
+                w[p + "left.out"] = f32(p + "mix.left.out", (W,))
+                w[p + "right.out"] = f32(p + "mix.right.out", (W,))
             else:
                 HD, HV = m.heads * m.dim, m.heads * m.vdim
                 w[p + "in"] = lin(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g", shape=(2 * HD + 2 * HV, W))
@@ -254,14 +304,19 @@ class HybridModel:
                 w[p + "decay"] = torch.tensor(m.decay, dtype=torch.float32, device=dev)
             f = layer.mlp
             if f is not None:
-                w[p + "norm2"] = norm_w(p + "norm2")
+                if not shared:
+                    w[p + "norm2"] = norm_w(p + "norm2")
                 if pre:
                     w[p + "canon2"] = f32(p + "canon2", (W, s.conv_taps))
                 if f.kind == "dense":
                     w[p + "up"] = lin(p + "mlp.up", shape=(f.ff, W))
                     w[p + "down"] = lin(p + "mlp.down", shape=(W, f.ff))
+                    if f.act == "xielu":
+                        w[p + "act"] = f32(p + "mlp.act", (2,))
                     continue
                 w[p + "router"] = f32(p + "mlp.router", (f.experts, W))
+                if f.correction:
+                    w[p + "correction"] = f32(p + "mlp.correction", (f.experts,))
                 for part, shape in (("gate", (f.ff, W)), ("up", (f.ff, W)), ("down", (W, f.ff))):
                     if part == "gate" and f.act != "silu_gate":
                         continue
@@ -276,7 +331,7 @@ class HybridModel:
 
         def get(name):
             shape = self.tensor_shapes()[name]
-            if name.endswith(("norm1", "norm2", "final.norm")) and self.spec.block in ("pre_norm", "parallel"):
+            if name.endswith(("norm1", "norm2", "final.norm")) and self.spec.block in ("pre_norm", "parallel") and not self.spec.plain_norms:
                 return 0.1 * torch.randn(shape, generator=g)            # stored as the deviation from one
             if name.endswith((".conv", ".conv.b")):
                 return torch.randn(shape, generator=g) / (shape[-1] if name.endswith(".conv") else 10.0)
@@ -286,8 +341,18 @@ class HybridModel:
                 return torch.log(torch.expm1(0.001 + 0.099 * torch.rand(shape, generator=g)))
             if name.endswith(".D"):
                 return torch.ones(shape)
-            if name.endswith(("norm1", "norm2", ".norm")):
+            if name.endswith(("norm1", "norm2", ".norm", ".out")):
                 return 1.0 + 0.1 * torch.randn(shape, generator=g)
+            if name.endswith("shift") or ".mu." in name:
+                return torch.rand(shape, generator=g)
+            if name.endswith(".w0"):                                     # decays exp(-exp(w0 + ...)) between about 0.37 and 0.998
+                return -6.0 + 6.0 * torch.rand(shape, generator=g)
+            if name.endswith(".u"):
+                return 0.5 * torch.randn(shape, generator=g)
+            if name.endswith("mlp.act"):
+                return torch.tensor([0.5, -0.5])
+            if name.endswith("correction"):
+                return 0.1 * torch.randn(shape, generator=g)
             if name.endswith(("canon1", "canon2")):
                 return torch.randn(shape, generator=g) / taps
             if name.endswith((".r1", ".r2")):
@@ -314,14 +379,36 @@ class HybridModel:
         if not s.tied_head:
             out["head"] = (s.vocab, W)
         out["final.norm"] = (W,)
+        if s.bigram is not None:
+            out["bigram"] = (s.bigram.buckets + 1, W)
         if s.max_positions:
             out["pos"] = (s.max_positions, W)
         if s.loop is not None:
             out["loop.step"] = (s.loop[2], W)
+        shared = s.block == "shared_norm"
+
+        def window_shapes(ck, m):
+            HD, GD, GV, HV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
+            out.update({ck + "q": (HD, W), ck + "k": (GD, W), ck + "v": (GV, W), ck + "o": (W, HV)})
+            if m.bias:
+                out.update({ck + "q.b": (HD,), ck + "k.b": (GD,), ck + "v.b": (GV,)})
+            if m.qk_norm:
+                out.update({ck + "q.norm": (m.dim,) if m.head_norm else (HD,), ck + "k.norm": (m.dim,) if m.head_norm else (GD,)})
+            if m.distance_bias:
+                out.update({ck + "r1": (m.heads,), ck + "r2": (m.heads,)})
+            if m.talking_heads:
+                out[ck + "talk"] = (m.heads, m.heads)
+            if m.sink:
+                out[ck + "sink"] = (m.heads,)
+            if m.gate:
+                out[ck + "g"] = (m.heads if m.gate_per_head else HV, W)
+
         for i, layer in enumerate(s.layers):
             p, m = f"l{i}.", layer.mixer
             out[p + "norm1"] = (W,)
-            if not par:
+            if shared:
+                out[p + "shift"] = (W,)
+            elif not par:
                 out[p + "canon1"] = (W, s.conv_taps)
             if s.block == "post_norm":
                 out[p + "dwa"] = (i + 2,)
@@ -340,31 +427,33 @@ class HybridModel:
                             p + "mix.uk": (m.heads * m.dim, m.kv_rank), p + "mix.uv": (HV, m.kv_rank), p + "mix.sink": (m.heads,),
                             p + "mix.g": (HV, W), p + "mix.o": (W, HV)})
             elif m.kind == "window_attention":
-                HD, GD, GV, HV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
-                out.update({p + "mix.q": (HD, W), p + "mix.k": (GD, W), p + "mix.v": (GV, W), p + "mix.o": (W, HV)})
-                if m.bias:
-                    out.update({p + "mix.q.b": (HD,), p + "mix.k.b": (GD,), p + "mix.v.b": (GV,)})
-                if m.qk_norm:
-                    out.update({p + "mix.q.norm": (HD,), p + "mix.k.norm": (GD,)})
-                if m.distance_bias:
-                    out.update({p + "mix.r1": (m.heads,), p + "mix.r2": (m.heads,)})
-                if m.talking_heads:
-                    out[p + "mix.talk"] = (m.heads, m.heads)
-                if m.gate:
-                    out[p + "mix.g"] = (HV, W)
+                window_shapes(p + "mix.", m)
+            elif m.kind == "paired":
+                window_shapes(p + "mix.left.", m.left)
+                R, ck = m.right, p + "mix.right."
+                HD = R.heads * R.dim
+                out.update({ck + k: (HD, W) for k in "rkvg"})
+                out.update({ck + "mu." + k: (W,) for k in "rkvgw"})
+                out.update({ck + "w1": (R.rank, W), ck + "w2": (HD, R.rank), ck + "w0": (HD,), ck + "u": (R.heads, R.dim), ck + "norm": (HD,),
+                            ck + "o": (W, HD), p + "mix.left.out": (W,), p + "mix.right.out": (W,)})
             else:
                 HD, HV = m.heads * m.dim, m.heads * m.vdim
                 out.update({p + "mix.q": (HD, W), p + "mix.k": (HD, W), p + "mix.v": (HV, W), p + "mix.g": (HV, W),
                             p + "mix.o": (W, HV), p + "mix.norm": (HV,)})
             f = layer.mlp
             if f is not None:
-                out[p + "norm2"] = (W,)
+                if not shared:
+                    out[p + "norm2"] = (W,)
                 if pre:
                     out[p + "canon2"] = (W, s.conv_taps)
                 if f.kind == "dense":
                     out.update({p + "mlp.up": (f.ff, W), p + "mlp.down": (W, f.ff)})
+                    if f.act == "xielu":
+                        out[p + "mlp.act"] = (2,)
                     continue
                 out[p + "mlp.router"] = (f.experts, W)
+                if f.correction:
+                    out[p + "mlp.correction"] = (f.experts,)
                 for e in range(f.experts):
                     if f.act == "silu_gate":
                         out[f"{p}mlp.e{e}.gate"] = (f.ff, W)
@@ -410,6 +499,10 @@ class HybridModel:
         st = self._stream()
         if s.max_positions and max_pos >= s.max_positions:
             raise ValueError(f"position {max_pos}: the model has {s.max_positions} learned positions")
+        if s.block == "shared_norm":
+            return self._step_shared_norm(n=n, batch=batch, tokens=tokens, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot,
+                                          block_ptrs=block_ptrs, cu_blocks=cu_blocks, state=state, rows=rows, n_rows=n_rows,
+                                          max_pos=max_pos, trace=trace)
         if s.block == "parallel":
             return self._step_parallel(n=n, batch=batch, tokens=tokens, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot,
                                        block_ptrs=block_ptrs, cu_blocks=cu_blocks, state=state, rows=rows, n_rows=n_rows, max_pos=max_pos,
@@ -549,6 +642,110 @@ class HybridModel:
                                               dt, st), "group_norm_rows")
             return self._logits(xn)
 
+    def _step_shared_norm(self, *, n, batch, tokens, tok_seq, tok_pos, cu_q, seq_slot, block_ptrs, cu_blocks, state, rows, n_rows, max_pos,
+                          trace=None):
+        """The step of shared-norm blocks: h = n(x), x <- x + mixer(shift(h)) + ff(h) per run.  One kernel per run takes the previous
+        run's outputs (the two sides of a paired mixer, each normed over the width, and the feed-forward's) into the float stream and
+        emits this run's normed rows; one kernel shifts them (and forms the recurrence's blends) against the previous token's."""
+        s, lib, w, dev, T, dt = self.spec, self.lib, self.w, self.device, self.T, self.dt
+        W, eps, st = s.width, s.norm_eps, self._stream()
+        c = StepArrays(n=n, batch=batch, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot, block_ptrs=block_ptrs,
+                       cu_blocks=cu_blocks, state=state, max_pos=max_pos)
+        stride = state.storage.stride(0)
+        x = torch.empty(n, W, dtype=torch.float32, device=dev)
+        with self.timed("embed"):
+            if s.bigram is not None:
+                b = s.bigram
+                H.check(lib.b200h_embed_hashed(tokens.data_ptr(), w["embed"].data_ptr(), w["bigram"].data_ptr(), b.buckets, b.mul_prev,
+                                               b.mul_cur, state.ptr(self.token_off), stride, tok_seq.data_ptr(), tok_pos.data_ptr(),
+                                               cu_q.data_ptr(), seq_slot.data_ptr(), x.data_ptr(), n, batch, W, dt, st), "embed_hashed")
+            else:
+                H.check(lib.b200h_embed(tokens.data_ptr(), w["embed"].data_ptr(), s.embedding_scale, x.data_ptr(), n, W, dt, st), "embed")
+        h = torch.empty(n, W, dtype=T, device=dev)
+        hf = torch.empty(n, W, dtype=torch.float32, device=dev)
+        sides = ff = None                # the previous run's outputs that the stream has not taken in yet
+        ff_f32, parts = 0, 0
+
+        def join(norm):
+            left, right, wl, wr = sides if sides is not None else (None, None, None, None)
+            with self.timed("residual + side norms + norm"):
+                H.check(lib.b200h_branch_residual_norm(
+                    x.data_ptr(), None if left is None else left.data_ptr(), None if right is None else right.data_ptr(),
+                    None if wl is None else wl.data_ptr(), None if wr is None else wr.data_ptr(), 0.5,
+                    None if ff is None else ff.data_ptr(), ff_f32, parts, None if norm is None else norm.data_ptr(), n, W, eps,
+                    None if norm is None else h.data_ptr(), None if norm is None else hf.data_ptr(), dt, st), "branch_residual_norm")
+
+        for r, (i, _) in enumerate(self.runs):
+            p, layer = f"l{i}.", s.layers[i]
+            join(w[p + "norm1"])
+            m = layer.mixer
+            if m.kind != "paired":
+                raise NotImplementedError(f"shared-norm blocks with a {m.kind!r} mixer")
+            nmu = 5
+            a = torch.empty(n, W, dtype=T, device=dev)
+            blends = torch.empty(nmu, n, W, dtype=T, device=dev)
+            with self.timed("token shift + blends"):
+                H.check(lib.b200h_token_shift(hf.data_ptr(), w[p + "shift"].data_ptr(), w[p + "right.mu"].data_ptr(), nmu,
+                                              state.ptr(self.shift_off[r]), stride, tok_seq.data_ptr(), cu_q.data_ptr(), seq_slot.data_ptr(),
+                                              n, batch, W, a.data_ptr(), blends.data_ptr(), dt, st), "token_shift")
+            y = self.window_mixer(i, a, c, run=r, m=m.left, p=p + "left.")
+            with self.timed("gemm out"):
+                left = self._linear(y, w[p + "left.o"])
+            y = self.channel_decay_mixer(i, blends, c, run=r, m=m.right, p=p + "right.")
+            with self.timed("gemm out"):
+                right = self._linear(y, w[p + "right.o"])
+            sides = (left, right, w[p + "left.out"], w[p + "right.out"])
+            f = layer.mlp
+            ff, ff_f32, parts = None, 0, 0
+            if f is not None:
+                if f.kind == "dense":
+                    ff, parts = self.dense_mlp(i, h), 1
+                else:
+                    ff, ff_f32, parts = self.routed_experts(i, hf, h, n), 1, f.top
+            if trace is not None:
+                join(None)
+                sides = ff = None
+                parts = 0
+                trace.append(x.clone())
+        xn = torch.empty(n_rows, W, dtype=T, device=dev)
+        with self.timed("final norm + head"):
+            if sides is not None or ff is not None:
+                join(None)
+            H.check(lib.b200h_group_norm_rows(x.data_ptr(), rows.data_ptr(), w["final.norm"].data_ptr(), n_rows, W, 1, eps, xn.data_ptr(),
+                                              dt, st), "group_norm_rows")
+            return self._logits(xn)
+
+    def channel_decay_mixer(self, i, blends, c, run=None, m=None, p=None):
+        """Channel-decay recurrence of layer i over the five blends [5, n, width] (T; for r, k, v, the gate and the decay): one batched
+        product for r | k | v | g, the decay's two small products around a tanh, the per-channel decays and the per-head recurrence on
+        the sequence's float state, then the per-head unit norm, its weight and silu(g).  Returns [n, heads * dim] (T)."""
+        r = i if run is None else run
+        m = self.spec.layers[i].mixer if m is None else m
+        p = f"l{i}." if p is None else p
+        w, lib, dev, n, st = self.w, self.lib, self.device, c.n, self._stream()
+        HD = m.heads * m.dim
+        with self.timed("gemm in"):
+            proj = torch.bmm(blends[:4], w[p + "in"].transpose(1, 2))              # [4, n, HD]: r, k, v, g
+            low = self._linear(blends[4], w[p + "w1"])
+        with self.timed("tanh"):
+            H.check(lib.b200h_tanh(low.data_ptr(), low.numel(), self.dt, st), "tanh")
+        with self.timed("gemm decay"):
+            d = self._linear_f32(low, w[p + "w2"])
+        es = proj.element_size()
+        base, plane = proj.data_ptr(), n * HD * es
+        o = torch.empty(n, HD, dtype=torch.float32, device=dev)
+        decay = torch.empty(n, HD, dtype=torch.float32, device=dev)
+        with self.timed("channel-decay recurrence"):
+            H.check(lib.b200h_channel_decay_scan(base, base + plane, base + 2 * plane, HD, d.data_ptr(), w[p + "w0"].data_ptr(),
+                                                 w[p + "u"].data_ptr(), c.state.ptr(self.mix_off[r]), c.state.storage.stride(0),
+                                                 c.cu_q.data_ptr(), c.seq_slot.data_ptr(), n, c.batch, m.heads, m.dim, m.vdim,
+                                                 decay.data_ptr(), o.data_ptr(), self.dt, st), "channel_decay_scan")
+        y = torch.empty(n, HD, dtype=self.T, device=dev)
+        with self.timed("head norm + gate"):
+            H.check(lib.b200h_group_norm_gate(o.data_ptr(), w[p + "norm"].data_ptr(), base + 3 * plane, HD, n, HD, m.heads, H.GATE_ACT["silu"],
+                                              self.spec.norm_eps, y.data_ptr(), self.dt, st), "group_norm_gate")
+        return y
+
     def norm_conv_input(self, r, i, sub, x, pending, extra, c):
         """What sublayer `sub` (1: mixer, 2: feed-forward) of run r reads: first the stream takes in `pending` (the previous
         sublayer's output) and `extra` (a vector for all rows), then h = norm(x), then h + causal convolution of h over the
@@ -593,13 +790,15 @@ class HybridModel:
         ld = (keys + 255) // 256 * 256
         return min(ld, (window + 3) // 4 * 4) if window else ld
 
-    def window_mixer(self, i, h, c, run=None):
-        """Windowed attention of layer i: one stacked projection (q | k | v | gate), biases + RMS norm of q and k over their
-        whole projections + cache store in one kernel, then attention over the window of cached keys with capped scores, distance penalty,
-        recombination of the heads' softmax weights, and the output gate.  Returns [n, heads * vdim] (T)."""
+    def window_mixer(self, i, h, c, run=None, m=None, p=None):
+        """Windowed attention of layer i (m, p: the spec and weight prefix of one side of a paired mixer): one stacked projection
+        (q | k | v | gate); biases + RMS norm of q and k (over their whole projections, or per head followed by a rotation) + cache
+        store in one kernel; then attention over the window or chunk of cached keys with capped scores, distance penalty, the heads'
+        scores or softmax weights recombined, a sink, and the output gate.  Returns [n, heads * vdim] (T)."""
         r = i if run is None else run
-        m, w, lib, dev, T, n = self.spec.layers[i].mixer, self.w, self.lib, self.device, self.T, c.n
-        p = f"l{i}."
+        m = self.spec.layers[i].mixer if m is None else m
+        p = f"l{i}." if p is None else p
+        w, lib, dev, T, n = self.w, self.lib, self.device, self.T, c.n
         HD, GD, GV, HV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
         with self.timed("gemm in"):
             proj = self._linear(h, w[p + "in"])
@@ -607,7 +806,8 @@ class HybridModel:
         f32 = dict(dtype=torch.float32, device=dev)
         a = H.WindowArgs()
         a.n, a.heads, a.kv_heads, a.dim, a.vdim, a.block_len, a.window = n, m.heads, m.kv_heads, m.dim, m.vdim, self.block_len, m.window
-        a.splits = self.window_splits(n, m.window, c.max_pos)
+        a.chunk, a.talk_scores, a.gate_heads = m.chunk, int(m.talk_scores), int(m.gate_per_head)
+        a.splits = self.window_splits(n, m.span, c.max_pos)
         a.scale, a.softcap, a.eps = m.scale, m.softcap, self.spec.norm_eps
         a.q, a.k, a.v, a.ld = base, base + es * HD, base + es * (HD + GD), ld
         if m.bias:
@@ -620,15 +820,24 @@ class HybridModel:
             a.r1, a.r2 = w[p + "r1"].data_ptr(), w[p + "r2"].data_ptr()
         if m.talking_heads:
             a.talk = w[p + "talk"].data_ptr()
+        if m.sink:
+            a.sink = w[p + "sink"].data_ptr()
         if m.gate:
             a.gate, a.ld_gate = base + es * (HD + GD + GV), ld
         y = torch.empty(n, HV, dtype=T, device=dev)
         a.tok_seq, a.tok_pos = c.tok_seq.data_ptr(), c.tok_pos.data_ptr()
         a.block_ptrs, a.cu_blocks = c.block_ptrs.data_ptr(), c.cu_blocks.data_ptr()
         a.layer_off, a.v_off, a.dtype, a.stream = self.cache_off[r], self.v_off[r], self.dt, self._stream()
-        with self.timed("qk norm + cache store"):
-            H.check(lib.b200h_window_prep(C.byref(a)), "window_prep")
-        self._window_attend(a, m, c, qn, y, "windowed attention")
+        if m.head_norm or m.rot is not None:
+            if m.qk_norm and not m.head_norm:
+                raise NotImplementedError("rotation after a norm over the whole projection")
+            rot = H.Rotary(w[p + "freqs"].data_ptr(), m.rot.dims // 2, w[p + "mag"]) if m.rot is not None else H.Rotary(None, 0, 1.0)
+            with self.timed("head norm + rotate + cache store"):
+                H.check(lib.b200h_head_rope_prep(C.byref(a), C.byref(rot)), "head_rope_prep")
+        else:
+            with self.timed("qk norm + cache store"):
+                H.check(lib.b200h_window_prep(C.byref(a)), "window_prep")
+        self._window_attend(a, m, c, qn, y, "chunked attention" if m.chunk else "windowed attention")
         return y
 
     def _window_attend(self, a, m, c, qn, y, name):
@@ -638,7 +847,7 @@ class HybridModel:
         `window_scratch_bytes`."""
         n, HD, HV, es = c.n, m.heads * m.dim, m.heads * m.vdim, y.element_size()
         f32 = dict(dtype=torch.float32, device=self.device)
-        a.score_ld = self.window_score_ld(m.window, c.max_pos)
+        a.score_ld = self.window_score_ld(getattr(m, "span", m.window), c.max_pos)
         chunk = max(4, self.window_scratch_bytes // (4 * m.heads * a.score_ld) // 4 * 4)
         rows = min(n, chunk)
         scores = torch.empty(rows, m.heads, a.score_ld, **f32)
@@ -724,12 +933,15 @@ class HybridModel:
     def dense_mlp(self, i, h):
         """Dense feed-forward of layer i over its input h [n, width] (T): down(act(up h)) -> [n, width] (T)."""
         f, w = self.spec.layers[i].mlp, self.w
-        if f.act != "relu2":
+        if f.act not in ("relu2", "xielu"):
             raise NotImplementedError(f"activation {f.act!r}")
         with self.timed("gemm up"):
             a = self._linear(h, w[f"l{i}.up"])
-        with self.timed("squared relu"):
-            H.check(self.lib.b200h_relu2(a.data_ptr(), a.numel(), self.dt, self._stream()), "relu2")
+        with self.timed("activation"):
+            if f.act == "xielu":
+                H.check(self.lib.b200h_xielu(a.data_ptr(), a.numel(), w[f"l{i}.act"].data_ptr(), self.dt, self._stream()), "xielu")
+            else:
+                H.check(self.lib.b200h_relu2(a.data_ptr(), a.numel(), self.dt, self._stream()), "relu2")
         with self.timed("gemm down"):
             return self._linear(a, w[f"l{i}.down"])
 
@@ -742,13 +954,16 @@ class HybridModel:
         return out
 
     def _head_product(self, xn):
-        head = self.w["head"]
-        if self.T is torch.float32 or xn.device.type != "cuda":
-            return torch.mm(xn.float(), head.float().t())
+        return self._linear_f32(xn, self.w["head"])
+
+    def _linear_f32(self, x, wt):
+        """x wt^T with a float result (bf16 operands accumulate and stay in float)."""
+        if self.T is torch.float32 or x.device.type != "cuda":
+            return torch.mm(x.float(), wt.float().t())
         try:
-            return torch.mm(xn, head.t(), out_dtype=torch.float32)
+            return torch.mm(x, wt.t(), out_dtype=torch.float32)
         except RuntimeError:            # a shape the float-output GEMM refuses: float operands (same values, wider reads)
-            return torch.mm(xn.float(), head.float().t())
+            return torch.mm(x.float(), wt.float().t())
 
     # ---- the mechanisms, one method each (the step above strings them together; tests call them alone)
     def attention_splits(self, n, heads, max_pos):
@@ -766,8 +981,10 @@ class HybridModel:
         for l in self.spec.layers:
             if l.mixer.kind == "latent_attention":
                 key.append(self.attention_splits(n, l.mixer.heads, max_pos))
-            elif l.mixer.kind in ("window_attention", "conv_attention"):
-                key.append((self.window_splits(n, l.mixer.window, max_pos), self.window_score_ld(l.mixer.window, max_pos)))
+            elif l.mixer.kind in ("window_attention", "conv_attention", "paired"):
+                m = l.mixer.left if l.mixer.kind == "paired" else l.mixer
+                span = getattr(m, "span", m.window)
+                key.append((self.window_splits(n, span, max_pos), self.window_score_ld(span, max_pos)))
         return tuple(key)
 
     def conv_input(self, i, x, c, run=None, sub=1):
@@ -878,8 +1095,15 @@ class HybridModel:
         wts = torch.empty(n, f.top, dtype=torch.float32, device=dev)
         with self.timed("router"):
             src, src_dt = (xt, self.dt) if x is None else (x, H.F32)
-            H.check(lib.b200h_route_scored(src.data_ptr(), src_dt, w[p + "router"].data_ptr(), n, W, f.experts, f.top, H.SCORE_FN[f.score],
-                                           ids.data_ptr(), wts.data_ptr(), st), "route")
+            if f.grouped:
+                if f.score != "sigmoid":
+                    raise NotImplementedError("a router that chooses among groups scores with sigmoids")
+                H.check(lib.b200h_route_grouped(src.data_ptr(), src_dt, w[p + "router"].data_ptr(),
+                                                w[p + "correction"].data_ptr() if f.correction else None, n, W, f.experts, f.top, f.groups,
+                                                f.keep, f.group_top, int(f.renorm), f.scale, ids.data_ptr(), wts.data_ptr(), st), "route_grouped")
+            else:
+                H.check(lib.b200h_route_scored(src.data_ptr(), src_dt, w[p + "router"].data_ptr(), n, W, f.experts, f.top, H.SCORE_FN[f.score],
+                                               ids.data_ptr(), wts.data_ptr(), st), "route")
         out = torch.empty(n, f.top, W, dtype=torch.float32, device=dev)
         self.last_routing = (ids, wts)
         capturing = dev.type == "cuda" and torch.cuda.is_current_stream_capturing()      # the grouped path reads counts on the host

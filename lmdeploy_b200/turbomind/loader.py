@@ -283,6 +283,10 @@ class LazyCheckpoint:
     def get(self, name, default=None):
         return self[name] if name in self._shard_of else default
 
+    def shape(self, name):
+        """A tensor's shape from its shard's header (nothing is read)."""
+        return tuple(self._handle(self._shard_of[name]).get_slice(name).get_shape())
+
     def keys(self):
         return self._shard_of.keys()
 
@@ -323,7 +327,17 @@ def load_hybrid_checkpoint(cfg, tensors, *, name, block_len=64, max_batch=64, dt
     import dataclasses
     from .hybrid import HybridModel
     from .specs import HYBRID_ARCHITECTURES
-    spec = HYBRID_ARCHITECTURES[cfg["architecture"]](cfg, name=name)
+    import inspect
+    builder = HYBRID_ARCHITECTURES[cfg["architecture"]]
+    extra = {}
+    if "tensor_shapes" in inspect.signature(builder).parameters:          # a design some of whose sizes only tensor shapes give
+
+        class Shapes:
+            def __getitem__(self, key):
+                return tensors.shape(key) if hasattr(tensors, "shape") else tuple(tensors[key].shape)
+
+        extra["tensor_shapes"] = Shapes()
+    spec = builder(cfg, name=name, **extra)
     if dtype not in ("auto", "bfloat16", "float32"):
         raise ValueError(f"dtype {dtype!r}: hybrid decoders serve in bfloat16 or float32")
     spec = dataclasses.replace(spec, dtype="f32" if dtype == "float32" else "bf16")

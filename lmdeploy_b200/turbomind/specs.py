@@ -101,11 +101,12 @@ class RotarySpec:
     dims: int
     base: float
     scaling: tuple = None
+    linear: float = 1.0                 # every frequency is divided by this (positions stretched by a constant)
 
     def frequencies(self):
         """-> ([angle per position of pair i], factor on cos and sin), in double precision."""
         import math
-        f = [self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)]
+        f = [self.base ** (-2.0 * i / self.dims) / self.linear for i in range(self.dims // 2)]
         if self.scaling is None:
             return f, 1.0
         factor, original, fast, slow = self.scaling
@@ -167,7 +168,22 @@ class WindowAttentionSpec:
     distance_bias: bool = True    # per-head r1, r2
     talking_heads: bool = True    # [heads, heads] recombination of the softmax weights
     gate: bool = True
+    # switches of a design that rotates: the norm of q and k is PER HEAD over dim with a weight of dim entries shared by the heads,
+    # then interleaved pairs turn (rot); a row sees only the keys of its own chunk of `chunk` positions (counted from position 0);
+    # the [heads, heads] matrix mixes the heads' SCORES before the softmax instead of their weights after it; a learned score per
+    # head joins the softmax denominator (sink); the gate is ONE number per head.
+    head_norm: bool = False
+    rot: RotarySpec = None
+    chunk: int = 0
+    talk_scores: bool = False
+    sink: bool = False
+    gate_per_head: bool = False
     kind = "window_attention"
+
+    @property
+    def span(self):
+        """The most keys a row sees (0: all earlier positions)."""
+        return min(self.window, self.chunk) if self.window and self.chunk else (self.window or self.chunk)
 
 
 @dataclass(frozen=True)
@@ -219,6 +235,32 @@ class SsmSpec:
 
 
 @dataclass(frozen=True)
+class ChannelDecaySpec:
+    """Linear recurrence whose decay depends on the token, per head and key channel:
+        w_t = exp(-exp(W2 tanh(W1 b_w) + w0)),  o_t = (S + diag(u) k_t v_t^T)^T r_t,  S <- diag(w_t) S + k_t v_t^T
+    with S a [dim, dim] float matrix per head.  Each of r, k, v, the gate g and the decay reads its own blend b_s = a_t + (a_(t-1) -
+    a_t) * mu_s of the mixer's input with the previous token's; every head's o is divided by its root mean square, times a
+    weight, times silu(W_g b_g), then projected.  `rank` is the inner size of the decay's two matrices."""
+    heads: int
+    dim: int
+    rank: int
+    kind = "channel_decay"
+
+    @property
+    def vdim(self):
+        return self.dim
+
+
+@dataclass(frozen=True)
+class PairedMixerSpec:
+    """Two mixers side by side on the same input, each with an output projection of its own; the result is
+    (rms(left) * w_left + rms(right) * w_right) / 2 with RMS norms over the model width."""
+    left: object                        # WindowAttentionSpec
+    right: object                       # ChannelDecaySpec
+    kind = "paired"
+
+
+@dataclass(frozen=True)
 class RoutedExpertsSpec:
     experts: int
     top: int
@@ -226,20 +268,40 @@ class RoutedExpertsSpec:
     score: str = "softmax"        # router scores: 'softmax' over all experts | 'sigmoid' of every logit on its own
     act: str = "silu_gate"        # expert: 'silu_gate' = down(silu(gate h) * up h) | 'relu2' = down(relu(up h)^2), no gate matrix
     scale_input: bool = False     # the router's score multiplies the expert's input instead of its output
+    # a router that chooses among groups (score 'sigmoid' only): a learned correction joins the scores for the CHOICE; the experts form
+    # `groups` equal groups of neighbours, a group's score is the sum of its `group_top` largest choice scores and only the `keep` best
+    # groups stay eligible; the chosen experts' scores are divided by their sum (renorm) and multiplied by `scale`.
+    grouped: bool = False
+    correction: bool = False
+    groups: int = 1
+    keep: int = 1
+    group_top: int = 2
+    renorm: bool = False
+    scale: float = 1.0
     kind = "moe"
 
 
 @dataclass(frozen=True)
 class DenseMlpSpec:
-    """down(act(up h)); act 'relu2' = the square of relu."""
+    """down(act(up h)); act 'relu2' = the square of relu; 'xielu' = softplus(p) z^2 + z / 2 for z > 0 and
+    (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise, with the two learned numbers p, q of the layer's 'mlp.act'."""
     ff: int
     act: str = "relu2"
     kind = "dense"
 
 
 @dataclass(frozen=True)
+class HashedBigramSpec:
+    """A second embedding table added to the first: row (previous token * mul_prev + token * mul_cur) mod buckets, and row `buckets`
+    (the last of buckets + 1) for a sequence's first token."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+
+
+@dataclass(frozen=True)
 class HybridLayerSpec:
-    mixer: object                       # LatentAttentionSpec | DecayAttentionSpec | WindowAttentionSpec | ConvAttentionSpec | SsmSpec
+    mixer: object                       # Latent / Decay / Window / Conv attention spec | SsmSpec | PairedMixerSpec
     mlp: object = None                  # RoutedExpertsSpec | DenseMlpSpec | None: the layer has no feed-forward
 
 
@@ -269,6 +331,10 @@ class HybridSpec:
     logit_softcap: float = 0.0          # > 0: logits <- cap * tanh(logits / cap)
     tied_head: bool = False             # the head is the embedding table (no 'head' tensor)
     loop_readds_embedding: bool = False  # every pass of the loop but the first adds the embedding output to the stream before its vector
+    # 'shared_norm' blocks: ONE norm per layer, x <- x + mixer(shift(n(x))) + ff(n(x)): the mixer reads the normed row blended with the
+    #              previous token's normed row (h + (h' - h) * shift, a learned vector per layer), the feed-forward the row itself.
+    plain_norms: bool = False           # norm weights are stored as the full factor also in pre-norm / parallel / shared-norm blocks
+    bigram: HashedBigramSpec = None     # the embedding adds a hashed row of a second table chosen by the previous token
     hybrid = True
 
     @property
@@ -393,5 +459,52 @@ def lifuzen_spec(cfg, name="lifuzen"):
                       tied_head=True, loop_readds_embedding=True)
 
 
+def _fogizen_left(m):
+    heads, kv_heads, dim = int(m["heads"]), int(m["kv_heads"]), int(m["dim"])
+    if heads % kv_heads:
+        raise ValueError(f"{heads} query heads do not divide into {kv_heads} key/value heads")
+    r = m["rot"]
+    rot = RotarySpec(int(r["dims"]), float(r["base"]), linear=float((r.get("scaling") or {}).get("factor") or 1.0))
+    if rot.dims > dim or rot.dims % 2:
+        raise ValueError(f"rot.dims {rot.dims} (even) does not fit dim {dim}")
+    return WindowAttentionSpec(heads, kv_heads, dim, int(m.get("vdim", dim)), float(m["scale"]), qk_norm=True, bias=True,
+                               distance_bias=False, talking_heads=True, gate=True, head_norm=True, rot=rot,
+                               chunk=int((m.get("mask") or {}).get("size") or 0), talk_scores=True, sink=True, gate_per_head=True)
+
+
+def fogizen_spec(cfg, name="fogizen", tensor_shapes=None):
+    """config.json of a Fogizen checkpoint -> HybridSpec.  Every size and constant is read from the config; the inner size of the
+    decay's two matrices is a tensor's shape ('l<i>.mix.right.w1': [rank, width])."""
+    layers = []
+    for i, entry in enumerate(cfg["layers"]):
+        if entry["type"] != "parallel":
+            raise NotImplementedError(f"mixer type {entry['type']!r}")
+        right = entry["mixer"]["right"]
+        rank = int(right["rank"]) if "rank" in right else (int(tensor_shapes[f"l{i}.mix.right.w1"][0]) if tensor_shapes else 0)
+        if rank < 1:
+            raise ValueError(f"layer {i}: the decay's inner size is neither in the config nor a known tensor shape")
+        mixer = PairedMixerSpec(_fogizen_left(entry["mixer"]["left"]), ChannelDecaySpec(int(right["heads"]), int(right["dim"]), rank))
+        mlp = entry.get("mlp")
+        if mlp is not None:
+            if mlp["kind"] == "dense":
+                mlp = DenseMlpSpec(int(mlp["ff"]), act="xielu")
+            elif mlp["kind"] == "moe":
+                r = mlp["router"]
+                g = r.get("groups") or {}
+                mlp = RoutedExpertsSpec(int(r["experts"]), int(r["top"]), int(mlp["expert"]["ff"]), score="sigmoid", grouped=True,
+                                        correction=True, groups=int(g.get("count", 1)), keep=int(g.get("keep", g.get("count", 1))),
+                                        renorm=True, scale=float(r.get("scale", 1.0)))
+                if mlp.experts % mlp.groups or not 1 <= mlp.keep <= mlp.groups or not 1 <= mlp.top <= mlp.keep * (mlp.experts // mlp.groups):
+                    raise ValueError(f"layer {i}: top {mlp.top} of {mlp.experts} experts in {mlp.groups} groups of which {mlp.keep} stay")
+            else:
+                raise NotImplementedError(f"feed-forward kind {mlp['kind']!r}")
+        layers.append(HybridLayerSpec(mixer, mlp))
+    b = (cfg.get("embedding") or {}).get("bigram")
+    bigram = HashedBigramSpec(int(b["buckets"]), int(b["mul_prev"]), int(b["mul_cur"])) if b else None
+    return HybridSpec(name=name, arch="fogizen", width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=tuple(layers),
+                      norm_eps=float(cfg["norm"]["eps"]), norm_groups=1, conv_taps=1, embedding_scale=1.0,
+                      session_len=int(cfg.get("session_len", 0)), block="shared_norm", plain_norms=True, bigram=bigram)
+
+
 # config.json "architecture" -> spec builder, for checkpoints that are not HF `architectures` configs
-HYBRID_ARCHITECTURES = {"Gulozen": gulozen_spec, "Bodopel": bodopel_spec, "Lifuzen": lifuzen_spec}
+HYBRID_ARCHITECTURES = {"Gulozen": gulozen_spec, "Bodopel": bodopel_spec, "Lifuzen": lifuzen_spec, "Fogizen": fogizen_spec}

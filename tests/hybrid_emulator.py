@@ -283,21 +283,29 @@ class EmulatedHybridLib:
         rep = H // G
         qn = _f(a.qn, a.n, H, D)
         y = _f(a.y, a.n, H * V)
-        gate = _rows(a.gate, a.n, a.ld_gate, H * V) if a.gate else None
+        gate = _rows(a.gate, a.n, a.ld_gate, H if a.gate_heads else H * V) if a.gate else None
         seqs, poss = _i(a.tok_seq, a.n), _i(a.tok_pos, a.n)
         for t in range(a.n):
             s, pos = int(seqs[t]), int(poss[t])
             lo = max(0, pos - a.window + 1) if a.window > 0 else 0
+            if a.chunk > 0:
+                lo = max(lo, pos // a.chunk * a.chunk)
             ks, vs = zip(*[self._kv(a, s, j) for j in range(lo, pos + 1)])
             ks, vs = np.stack(ks), np.stack(vs)                                    # [L, G, D], [L, G, V]
             dist = (pos - np.arange(lo, pos + 1)).astype(np.float32)
             wts = np.zeros((H, len(dist)), np.float32)
+            raw = np.zeros((H, len(dist)), np.float32)
             for h in range(H):
                 sc = (ks[:, h // rep] @ qn[t, h]) * np.float32(a.scale)
                 if a.softcap > 0:
                     sc = a.softcap * np.tanh(sc / a.softcap)
                 if a.r1:
                     sc = sc - _f(a.r1, H)[h] * np.log1p(_f(a.r2, H)[h] * dist)
+                raw[h] = sc
+            if a.talk and a.talk_scores:
+                raw = _f(a.talk, H, H) @ raw
+            for h in range(H):
+                sc = raw[h]
                 if a.sink:
                     mx = max(float(sc.max()), float(_f(a.sink, H)[h]))
                     e = np.exp(sc - mx)
@@ -305,10 +313,155 @@ class EmulatedHybridLib:
                 else:
                     e = np.exp(sc - sc.max())
                     wts[h] = e / e.sum()
-            if a.talk:
+            if a.talk and not a.talk_scores:
                 wts = _f(a.talk, H, H) @ wts
-            out = np.stack([wts[h] @ vs[:, h // rep] for h in range(H)]).reshape(H * V)
-            y[t] = out * _sigmoid(gate[t]) if gate is not None else out
+            out = np.stack([wts[h] @ vs[:, h // rep] for h in range(H)])
+            if gate is not None:
+                out = out * (_sigmoid(gate[t])[:, None] if a.gate_heads else _sigmoid(gate[t]).reshape(H, V))
+            y[t] = out.reshape(H * V)
+        return 0
+
+    def b200h_head_rope_prep(self, args, rot):
+        a, r = args._obj, rot._obj
+        assert a.dtype == F32
+        H, G, D, V = a.heads, a.kv_heads, a.dim, a.vdim
+        q, k, v = _rows(a.q, a.n, a.ld, H * D), _rows(a.k, a.n, a.ld, G * D), _rows(a.v, a.n, a.ld, G * V)
+        if a.bias:
+            b = _f(a.bias, (H + G) * D + G * V)
+            q, k, v = q + b[:H * D], k + b[H * D:(H + G) * D], v + b[(H + G) * D:]
+        q, k = q.reshape(a.n, H, D), k.reshape(a.n, G, D)
+        if a.q_norm:
+            q = _unit(q, a.eps) * _f(a.q_norm, D)
+        if a.k_norm:
+            k = _unit(k, a.eps) * _f(a.k_norm, D)
+
+        class WithRot:
+            pass
+        holder = WithRot()
+        holder.rot = r
+        seqs, poss = _i(a.tok_seq, a.n), _i(a.tok_pos, a.n)
+        qn = _f(a.qn, a.n, H, D)
+        for t in range(a.n):
+            qn[t] = self._rot(q[t], int(poss[t]), holder)
+            kd, vd = self._kv(a, int(seqs[t]), int(poss[t]))
+            kd[:] = self._rot(k[t], int(poss[t]), holder)
+            vd[:] = v[t].reshape(G, V)
+        return 0
+
+    # ---- shared-norm blocks: hashed bigram embedding, side norms + residual, token shift, channel-decay recurrence
+    def b200h_embed_hashed(self, tokens, table, second, buckets, mul_prev, mul_cur, prev, slot_stride, tok_seq, tok_pos, cu_q, seq_slot, out,
+                           n, batch, width, dtype, stream):
+        assert dtype == F32
+        tok, seqs, poss = _i(tokens, n), _i(tok_seq, n), _i(tok_pos, n)
+        cu, slots = _i(cu_q, batch + 1), _i(seq_slot, batch)
+        tab = _a(table, (int(tok.max()) + 1) * width).reshape(-1, width)
+        sec = _f(second, buckets + 1, width)
+        O = _f(out, n, width)
+        for t in range(n):
+            s = int(seqs[t])
+            row = buckets
+            if poss[t] > 0:
+                before = int(tok[t - 1]) if t > cu[s] else int(_i(int(prev) + 4 * int(slots[s]) * slot_stride, 1)[0])
+                row = (before * mul_prev + int(tok[t]) * mul_cur) % buckets
+            O[t] = tab[tok[t]] + sec[row]
+        for s in range(batch):
+            if cu[s] < cu[s + 1]:
+                _i(int(prev) + 4 * int(slots[s]) * slot_stride, 1)[0] = tok[cu[s + 1] - 1]
+        return 0
+
+    def b200h_branch_residual_norm(self, x, left, right, wl, wr, branch_scale, ff, ff_is_f32, parts, w, n, width, eps, h, hf, dtype, stream):
+        X = _f(x, n, width)
+        if left:
+            X += np.float32(branch_scale) * (_unit(_f(left, n, width), eps) * _f(wl, width) + _unit(_f(right, n, width), eps) * _f(wr, width))
+        if ff:
+            F = _f(ff, n, parts, width)
+            for p in range(parts):
+                X += F[:, p]
+        if w:
+            v = _unit(X, eps) * _f(w, width)
+            if h:
+                _f(h, n, width)[:] = v
+            if hf:
+                _f(hf, n, width)[:] = v
+        return 0
+
+    def b200h_token_shift(self, h, shift, mu, nmu, state, slot_stride, tok_seq, cu_q, seq_slot, n, batch, width, a, blends, dtype, stream):
+        Hm = _f(h, n, width)
+        sh = _f(shift, width) if shift else np.zeros(width, np.float32)
+        M = _f(mu, nmu, width) if nmu else None
+        cu, slots = _i(cu_q, batch + 1), _i(seq_slot, batch)
+        A = _f(a, n, width) if a else None
+        B = _f(blends, nmu, n, width) if nmu else None
+        for s in range(batch):
+            lo, hi = cu[s], cu[s + 1]
+            if lo == hi:
+                continue
+            st = _f(int(state) + 4 * int(slots[s]) * slot_stride, 2, width)
+            hp, ap = st[0].copy(), st[1].copy()
+            for t in range(lo, hi):
+                cur = Hm[t] + (hp - Hm[t]) * sh
+                if A is not None:
+                    A[t] = cur
+                for m in range(nmu):
+                    B[m, t] = cur + (ap - cur) * M[m]
+                hp, ap = Hm[t].copy(), cur
+            st[0], st[1] = hp, ap
+        return 0
+
+    def b200h_channel_decay_scan(self, r, k, v, ld, d, w0, bonus, state, slot_stride, cu_q, seq_slot, n, batch, heads, dim, vdim, decay, out,
+                                 dtype, stream):
+        R, K, Vv = _rows(r, n, ld, heads * dim), _rows(k, n, ld, heads * dim), _rows(v, n, ld, heads * vdim)
+        Wd = np.exp(-np.exp(_f(d, n, heads * dim) + _f(w0, heads * dim)))
+        U = _f(bonus, heads, dim)
+        O = _f(out, n, heads, vdim)
+        cu, slots = _i(cu_q, batch + 1), _i(seq_slot, batch)
+        for s in range(batch):
+            S = _f(int(state) + 4 * int(slots[s]) * slot_stride, heads, vdim, dim)            # [head][value][key]
+            for t in range(cu[s], cu[s + 1]):
+                for hh in range(heads):
+                    kk, rr = K[t, hh * dim:(hh + 1) * dim], R[t, hh * dim:(hh + 1) * dim]
+                    kv = np.outer(Vv[t, hh * vdim:(hh + 1) * vdim], kk)
+                    O[t, hh] = (S[hh] + kv * U[hh]) @ rr
+                    S[hh] = S[hh] * Wd[t, hh * dim:(hh + 1) * dim] + kv
+        return 0
+
+    def b200h_group_norm_gate(self, o, w, gate, ld_gate, n, count, groups, act, eps, y, dtype, stream):
+        G = _rows(gate, n, ld_gate, count)
+        g = G * _sigmoid(G) if act == 1 else _sigmoid(G)
+        _f(y, n, count)[:] = _unit(_f(o, n, groups, count // groups), eps).reshape(n, count) * _f(w, count) * g
+        return 0
+
+    def b200h_xielu(self, x, count, params, dtype, stream):
+        X, pr = _a(x, count), _a(params, 2)
+        sp = lambda z: np.log1p(np.exp(-abs(z))) + max(z, 0.0)
+        pos, neg = np.float32(sp(float(pr[0]))), np.float32(0.5 + sp(float(pr[1])))
+        z = X.copy()
+        X[:] = np.where(z > 0, pos * z * z + 0.5 * z, neg * (np.expm1(np.minimum(z, 0)) - z) + 0.5 * z)
+        return 0
+
+    def b200h_tanh(self, x, count, dtype, stream):
+        X = _a(x, count)
+        X[:] = np.tanh(X)
+        return 0
+
+    def b200h_route_grouped(self, x, x_dtype, router, correction, n, width, experts, top, groups, keep, group_top, renorm, scale, ids, wts,
+                            stream):
+        assert x_dtype == F32
+        sc = _sigmoid(_f(x, n, width) @ _f(router, experts, width).T)
+        ch = sc + _f(correction, experts) if correction else sc.copy()
+        per = experts // groups
+        if groups > 1 and keep < groups:
+            gs = -np.sort(-ch.reshape(n, groups, per), -1)[:, :, :group_top].sum(-1)
+            kept = np.argsort(-gs, -1, kind="stable")[:, :keep]
+            mask = np.zeros((n, groups), bool)
+            np.put_along_axis(mask, kept, True, -1)
+            ch = np.where(np.repeat(mask, per, -1), ch, -np.inf)
+        order = np.argsort(-ch, -1, kind="stable")[:, :top]
+        chosen = np.take_along_axis(sc, order, -1)
+        if renorm:
+            chosen = chosen / (chosen.sum(-1, keepdims=True) + np.float32(1e-20))
+        _i(ids, n * top).reshape(n, top)[:] = order
+        _f(wts, n, top)[:] = chosen * np.float32(scale)
         return 0
 
     # ---- parallel blocks, convolved rotary attention, state-space mixer
