@@ -44,9 +44,12 @@ def softplus(x):
 
 def embed(tokens, previous, w, cfg):
     """tokens: the ids of this call; previous: the id before the first of them (None at a sequence's start)."""
-    b = cfg["embedding"]["bigram"]
+    b = (cfg.get("embedding") or {}).get("bigram")
     rows = []
     for tok in tokens:
+        if b is None:                                   # a model without the second table
+            rows.append(w["embed"][tok])
+            continue
         row = b["buckets"] if previous is None else (previous * b["mul_prev"] + tok * b["mul_cur"]) % b["buckets"]
         rows.append(w["embed"][tok] + w["bigram"][row])
         previous = tok
@@ -80,7 +83,7 @@ def sink_softmax(s, sink):
     return e / (math.exp(float(sink) - m) + e.sum())
 
 
-def new_attention_state(m, dt):
+def new_attention_state(m, dt=torch.float64):
     G = m["kv_heads"]
     return dict(k=torch.zeros(0, G, m["dim"], dtype=dt), v=torch.zeros(0, G, m["vdim"], dtype=dt))
 
@@ -117,7 +120,7 @@ def chunk_attention(a, p, m, eps, positions, state):
     return out @ p["o"].T
 
 
-def new_recurrence_state(m, dt):
+def new_recurrence_state(m, dt=torch.float64):
     return dict(S=torch.zeros(m["heads"], m["dim"], m["dim"], dtype=dt))
 
 
