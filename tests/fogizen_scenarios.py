@@ -443,7 +443,7 @@ def side_norms_and_residual(make, tol):
     W, n, eps = cfg["width"], 37, cfg["norm"]["eps"]
     g = torch.Generator().manual_seed(9)
     r = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16).float()
-    x0, lf, rt, ff = r(n, W), 3.0 * r(n, W), 0.2 * r(n, W), r(n, 3, W)
+    x0, lf, rt, ff = r(n, W), 4.0 * r(n, W), 0.25 * r(n, W), r(n, 3, W)          # powers of two keep the values in bfloat16
     wl, wr, wn = w["l0.mix.left.out"].double(), w["l0.mix.right.out"].double(), w["l1.norm1"].double()
     xs = x0.double() + 0.5 * (F.unit_rms(lf.double(), eps) * wl + F.unit_rms(rt.double(), eps) * wr) + ff.double().sum(1)
     dev, T = model.device, model.T
