@@ -94,6 +94,24 @@ def lifuzen_bench_config(z):
                         "mlp": mlp} for t in HYBRID_LAYERS]}
 
 
+def fogizen_bench_config(z, chunk=1024):
+    """A Fogizen config.json (dict) of size `z`: four shared-norm layers whose paired mixer has the dense decoder's head geometry on
+    its attention side (GQA, 128 dimensions per head of which 64 turn, chunks of 1024 keys) and width / 64 recurrent heads of 64
+    channels (decay matrices of inner size 64) on the other; the first layer's feed-forward is dense with the active size of the
+    routed ones (top * ff), the others have eight gated experts in four groups of which two stay eligible and two experts are chosen."""
+    d = z["dense"]
+    left = {"heads": d["heads"], "kv_heads": d["kv_heads"], "dim": 128, "vdim": 128, "mask": {"size": chunk}, "scale": 128 ** -0.5,
+            "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 2.0}}}
+    right = {"heads": z["width"] // 64, "dim": 64, "rank": 64}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.0, "groups": {"count": z["experts"] // 2, "keep": z["experts"] // 4}}}
+    dense = {"kind": "dense", "ff": z["top"] * z["ff"]}
+    return {"architecture": "Fogizen", "norm": {"eps": 1e-6}, "vocab": HYBRID_VOCAB, "width": z["width"],
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "layers": [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": dense if i == 0 else moe}
+                       for i in range(len(HYBRID_LAYERS))]}
+
+
 def _hybrid_leg(torch, spec, batch, ctx, steps, warm, session, blocks):
     """One hybrid decoder through its engine: throughput, then per-operator device time (eight more decode steps, then one fresh
     4096-row prefill step, bracketed by CUDA events)."""
@@ -159,7 +177,7 @@ def run_hybrid(args):
     from lmdeploy_b200.messages import TurbomindEngineConfig
     from lmdeploy_b200.turbomind import ModelSpec
     from lmdeploy_b200.turbomind.engine import TurboMind
-    from lmdeploy_b200.turbomind.specs import bodopel_spec, gulozen_spec, lifuzen_spec
+    from lmdeploy_b200.turbomind.specs import bodopel_spec, fogizen_spec, gulozen_spec, lifuzen_spec
     z = HYBRID_SIZES[args.hybrid]
     batch, ctx, steps, warm = args.hybrid_batch, args.hybrid_ctx, args.steps, max(args.warmup, 3)
     session = 2 * ctx + warm + steps + 16
@@ -172,6 +190,8 @@ def run_hybrid(args):
             spec = bodopel_spec(bodopel_bench_config(z), name=f"bodopel-{args.hybrid}")
         elif args.hybrid_design == "lifuzen":
             spec = lifuzen_spec(lifuzen_bench_config(z), name=f"lifuzen-{args.hybrid}")
+        elif args.hybrid_design == "fogizen":
+            spec = fogizen_spec(fogizen_bench_config(z), name=f"fogizen-{args.hybrid}")
         else:
             spec = gulozen_spec(hybrid_config(z), name=f"gulozen-{args.hybrid}")
         out["hybrid"] = _hybrid_leg(torch, spec, batch, ctx, steps, warm, session, blocks)
@@ -179,6 +199,10 @@ def run_hybrid(args):
             # the closest existing model -- attention with a sink, a recurrent layer, routed experts -- at equal size, same workload
             out["closest"] = dict(_hybrid_leg(torch, gulozen_spec(hybrid_config(z), name=f"gulozen-{args.hybrid}"), batch, ctx, steps, warm,
                                               session, blocks), design="gulozen")
+        if args.hybrid_design == "fogizen":
+            # the closest existing model -- parallel blocks, two-pass attention with a sink, a scanned recurrence, sigmoid-routed experts
+            out["closest"] = dict(_hybrid_leg(torch, lifuzen_spec(lifuzen_bench_config(z), name=f"lifuzen-{args.hybrid}"), batch, ctx, steps,
+                                              warm, session, blocks), design="lifuzen")
         d = z["dense"]
         dspec = ModelSpec(f"dense-{args.hybrid}", "llama", d["hidden"], len(HYBRID_LAYERS), d["heads"], d["kv_heads"], d["inter"], HYBRID_VOCAB,
                           1e4, weight_format="fp16")
@@ -213,11 +237,12 @@ def parse():
     ap.add_argument("--hybrid", default=None, choices=list(HYBRID_SIZES),
                     help="instead of the default workload: prefill and decode tokens/s of a hybrid decoder of this size (--hybrid-design) "
                          "beside the dense decoder of equal size, both through the engine (random weights)")
-    ap.add_argument("--hybrid-design", default="gulozen", choices=["gulozen", "bodopel", "lifuzen"],
+    ap.add_argument("--hybrid-design", default="gulozen", choices=["gulozen", "bodopel", "lifuzen", "fogizen"],
                     help="which hybrid design --hybrid builds: Gulozen (latent / decayed linear attention, routed experts), Bodopel "
                          "(windowed attention with grouped key/value heads, dense feed-forward) or Lifuzen (parallel blocks: convolved rotary "
                          "attention with a sink / state-space mixer, sigmoid-routed squared-relu experts; also runs Gulozen of equal size, the "
-                         "closest existing model, beside it)")
+                         "closest existing model, beside it) or Fogizen (shared-norm blocks with token shift: chunked rotary attention beside a "
+                         "channel-decay recurrence in every layer, dense and group-routed experts; also runs Lifuzen of equal size beside it)")
     ap.add_argument("--hybrid-batch", type=int, default=32)
     ap.add_argument("--hybrid-ctx", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true", help="do not capture the step in a CUDA graph")

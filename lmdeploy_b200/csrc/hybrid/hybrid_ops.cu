@@ -1467,19 +1467,13 @@ B200H_API int b200h_channel_decay_scan(const void* r, const void* k, const void*
     cudaStream_t st = (cudaStream_t)stream;
     const int64_t count = (int64_t)n * heads * dim;
     channel_decay_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>((const float*)d, (const float*)w0, heads * dim, count, (float*)decay);
-    // two value columns per warp where the head has an even number of them (r, k and the decays are read once for both)
-    const int nc = vdim % 2 == 0 ? 2 : 1, units = vdim / nc, warps = units < 8 ? units : 8;
-    const dim3 grid((units + warps - 1) / warps, heads, batch), block(32, warps);
-    const int nw = (dim + 31) / 32;
-#define B200H_SCAN(NW, NC)                                                                                                                  \
-    channel_decay_scan_kernel<T, NW, NC><<<grid, block, 0, st>>>((const T*)r, (const T*)k, (const T*)v, ld, (const float*)decay,              \
-                                                                 (const float*)bonus, (float*)state, slot_stride, (const int*)cu_q,          \
-                                                                 (const int*)seq_slot, heads, dim, vdim, (float*)out)
-#define B200H_SCAN_NW(NC) \
-    do { if (nw <= 1) B200H_SCAN(1, NC); else if (nw <= 2) B200H_SCAN(2, NC); else if (nw <= 4) B200H_SCAN(4, NC); else B200H_SCAN(8, NC); } while (0)
-    B200H_DISPATCH_T(dtype, if (nc == 2) B200H_SCAN_NW(2); else B200H_SCAN_NW(1));
-#undef B200H_SCAN_NW
-#undef B200H_SCAN
+    // a block per (sequence, head, 32 value columns), a warp per 16 key channels
+    const int groups = (vdim + 31) / 32, kw = (dim + 15) / 16;
+    const dim3 grid(heads * groups, batch), block(32, kw);
+    const size_t smem = (size_t)kw * (3 * 4 * 16 + 2 * 4 * 32) * sizeof(float);
+    B200H_DISPATCH_T(dtype, (channel_decay_scan_kernel<T, 4><<<grid, block, smem, st>>>(
+        (const T*)r, (const T*)k, (const T*)v, ld, (const float*)decay, (const float*)bonus, (float*)state, slot_stride, (const int*)cu_q,
+        (const int*)seq_slot, heads, dim, vdim, (float*)out)));
     return launched("channel_decay_scan");
 }
 

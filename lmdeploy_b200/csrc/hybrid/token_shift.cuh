@@ -141,75 +141,125 @@ __global__ void channel_decay_kernel(const float* __restrict__ d, const float* _
 }
 
 // Per head, with S a [dim, vdim] float matrix per sequence:  o_t = (S + diag(u) k_t v_t^T)^T r_t,  S <- diag(w_t) S + k_t v_t^T.
-// The columns of S (one per value channel) are independent: one warp owns NC value columns of one (sequence, head); lane l keeps rows
-// (key channels) l, l + 32, ... of those columns in registers and walks the sequence's rows of this step in order; r_t, k_t and
-// the decays w_t are read once for the warp's NC columns.  r, k, v: T with row stride ld; decay: float [n, heads * dim].
-// State layout per head: [vdim][dim] floats.
-template <typename T, int NW, int NC>
-__global__ void channel_decay_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, int64_t ld,
-                                          const float* __restrict__ decay, const float* __restrict__ bonus, float* __restrict__ state,
-                                          int64_t slot_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads,
-                                          int dim, int vdim, float* __restrict__ out)
+// One block owns 32 value columns of one (sequence, head); its warps split the key channels, 16 each: lane j of warp w keeps
+// S[16 w .. 16 w + 15, j] in registers, so a row costs no shuffle per column.  With c = sum_i r_i u_i k_i (the bonus term, common to
+// all columns) a warp's part of a row is  sum_(its i) r_i S_ij + v_j c_(its i);  then S_ij <- w_i S_ij + k_i v_j.  The parts of R
+// rows meet in shared memory, one block barrier per R rows (the parts are double-buffered), and warp u % warps writes row u.
+// r_t, k_t and w_t of a warp's channels pass through the warp's own shared memory [3][R][16] (every lane reads them as 16-byte
+// broadcasts); the next R rows' global loads are in flight while the current ones are computed.
+// r, k, v: T with row stride ld; decay: float [n, heads * dim].  State layout per head: [vdim][dim] floats.
+// blockDim = (32, ceil(dim / 16)); grid = (heads * ceil(vdim / 32), batch).  Channels past dim hold zeros and stay zero.
+template <typename T, int R>
+__global__ void __launch_bounds__(512) channel_decay_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
+                                                                int64_t ld, const float* __restrict__ decay, const float* __restrict__ bonus,
+                                                                float* __restrict__ state, int64_t slot_stride, const int* __restrict__ cu_q,
+                                                                const int* __restrict__ seq_slot, int heads, int dim, int vdim,
+                                                                float* __restrict__ out)
 {
-    const int col = (blockIdx.x * blockDim.y + threadIdx.y) * NC, h = blockIdx.y, s = blockIdx.z, lane = threadIdx.x;
-    if (col >= vdim) return;
-    const int first = cu_q[s], last = cu_q[s + 1];
-    if (first == last) return;
-    float* sp = state + (int64_t)seq_slot[s] * slot_stride + ((size_t)h * vdim + col) * dim;
-    float st[NC][NW], ub[NW];
+    constexpr int CK = 16, E = R * CK / 32;                   // key channels per warp; staged elements per lane and array
+    static_assert(R * CK % 32 == 0 && 32 % CK == 0, "a warp stages whole rows");
+    extern __shared__ __align__(16) float cds_smem[];
+    const int lane = threadIdx.x, w = threadIdx.y, KW = blockDim.y, groups = (vdim + 31) / 32;
+    const int s = blockIdx.y, first = cu_q[s], last = cu_q[s + 1];
+    if (first == last) return;                                // the whole block leaves
+    const int h = blockIdx.x / groups, col = (blockIdx.x - h * groups) * 32 + lane, c0 = w * CK;
+    const bool live = col < vdim;
+    float* rs = cds_smem + (size_t)w * 3 * R * CK;
+    float* ks = rs + R * CK;
+    float* wd = ks + R * CK;
+    float* part = cds_smem + (size_t)KW * 3 * R * CK;         // [2][KW][R][32]
+    float* sp = state + (int64_t)seq_slot[s] * slot_stride + ((size_t)h * vdim + (live ? col : 0)) * dim + c0;
+    float S[CK];
+    const bool vec = dim % 4 == 0 && (reinterpret_cast<uintptr_t>(sp) & 15) == 0;
 #pragma unroll
-    for (int i = 0; i < NW; ++i) {
-        const int d = i * 32 + lane;
-        ub[i] = d < dim ? bonus[(size_t)h * dim + d] : 0.f;
+    for (int i = 0; i < CK; i += 4) {
+        if (vec && live && c0 + i < dim) {
+            const float4 q = *reinterpret_cast<const float4*>(sp + i);
+            S[i] = q.x; S[i + 1] = q.y; S[i + 2] = q.z; S[i + 3] = q.w;
+        } else {
 #pragma unroll
-        for (int c = 0; c < NC; ++c) st[c][i] = d < dim ? sp[(size_t)c * dim + d] : 0.f;
+            for (int e = 0; e < 4; ++e) S[i + e] = (live && c0 + i + e < dim) ? sp[i + e] : 0.f;
+        }
     }
-    const size_t hd = (size_t)heads * dim;
-    // four rows at a time: their loads do not depend on the state, only the four updates are in order
-    for (int t0 = first; t0 < last; t0 += 4) {
-        float ra[4][NW], ka[4][NW], wa[4][NW], va[4][NC];
+    // staged element e of a lane: row (e * 32 + lane) / CK of the group, the warp's channel (e * 32 + lane) % CK
+    const int my_d = c0 + lane % CK, my_u = lane / CK;
+    const bool my_in = my_d < dim;
+    const float ub = my_in ? bonus[(size_t)h * dim + my_d] : 0.f;
+    const size_t hd = (size_t)heads * dim, my_at = (size_t)h * dim + my_d;
+    float rr[E], kk[E], ww[E], vv[R];
+    // the loads of rows [t0, t0 + R) into registers (zeros past the sequence's last row and past dim)
+#define B200H_CDS_LOAD(t0)                                                                                        \
+    _Pragma("unroll") for (int e = 0; e < E; ++e) {                                                               \
+        const int u = e * (32 / CK) + my_u;                                                                       \
+        const bool in = my_in && (t0) + u < last;                                                                 \
+        const size_t t = (size_t)((t0) + u);                                                                      \
+        rr[e] = in ? to_f(r[t * ld + my_at]) : 0.f;                                                               \
+        kk[e] = in ? to_f(k[t * ld + my_at]) : 0.f;                                                               \
+        ww[e] = in ? decay[t * hd + my_at] : 0.f;                                                                 \
+    }                                                                                                             \
+    _Pragma("unroll") for (int u = 0; u < R; ++u)                                                                 \
+        vv[u] = (live && (t0) + u < last) ? to_f(v[(size_t)((t0) + u) * ld + (size_t)h * vdim + col]) : 0.f;
+    B200H_CDS_LOAD(first)
+    int p = 0;
+    for (int t0 = first; t0 < last; t0 += R, p ^= 1) {
+        float cc[R], vc[R];
+        __syncwarp();                                        // the previous rows' readers are done with the warp's shared memory
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            if (t0 + u < last) {                      // a step of one row (decode) loads one row
-                const size_t t = (size_t)(t0 + u);
+        for (int e = 0; e < E; ++e) {
+            const int at = e * 32 + lane;                    // = row * CK + channel
+            rs[at] = rr[e];
+            ks[at] = kk[e];
+            wd[at] = ww[e];
+            float c = rr[e] * ub * kk[e];                    // the bonus term of this warp's channels: summed over the CK lanes of a row
 #pragma unroll
-                for (int c = 0; c < NC; ++c) va[u][c] = to_f(v[t * ld + (size_t)h * vdim + col + c]);
+            for (int o = CK / 2; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
 #pragma unroll
-                for (int i = 0; i < NW; ++i) {
-                    const int d = i * 32 + lane;
-                    ra[u][i] = d < dim ? to_f(r[t * ld + (size_t)h * dim + d]) : 0.f;
-                    ka[u][i] = d < dim ? to_f(k[t * ld + (size_t)h * dim + d]) : 0.f;
-                    wa[u][i] = d < dim ? decay[t * hd + (size_t)h * dim + d] : 0.f;
-                }
-            }
+            for (int q = 0; q < 32 / CK; ++q) cc[e * (32 / CK) + q] = __shfl_sync(0xffffffffu, c, q * CK);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < R; ++u) vc[u] = vv[u];
+        __syncwarp();
+        B200H_CDS_LOAD(t0 + R)                               // in flight while the staged rows are computed
+        float* mine = part + ((size_t)(p * KW + w) * R) * 32 + lane;
+#pragma unroll
+        for (int u = 0; u < R; ++u) {
             if (t0 + u < last) {
-                float part[NC];
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+                const float vj = vc[u];
 #pragma unroll
-                for (int c = 0; c < NC; ++c) {
-                    part[c] = 0.f;
-#pragma unroll
-                    for (int i = 0; i < NW; ++i) {
-                        const float kv = ka[u][i] * va[u][c];                       // rows past dim hold zeros and stay zero
-                        part[c] = fmaf(ra[u][i], fmaf(ub[i], kv, st[c][i]), part[c]);
-                        st[c][i] = fmaf(wa[u][i], st[c][i], kv);
-                    }
+                for (int i = 0; i < CK; i += 4) {
+                    const float4 r4 = *reinterpret_cast<const float4*>(rs + u * CK + i);
+                    const float4 k4 = *reinterpret_cast<const float4*>(ks + u * CK + i);
+                    const float4 w4 = *reinterpret_cast<const float4*>(wd + u * CK + i);
+                    a0 = fmaf(r4.x, S[i], a0);     S[i] = fmaf(w4.x, S[i], k4.x * vj);
+                    a1 = fmaf(r4.y, S[i + 1], a1); S[i + 1] = fmaf(w4.y, S[i + 1], k4.y * vj);
+                    a2 = fmaf(r4.z, S[i + 2], a2); S[i + 2] = fmaf(w4.z, S[i + 2], k4.z * vj);
+                    a3 = fmaf(r4.w, S[i + 3], a3); S[i + 3] = fmaf(w4.w, S[i + 3], k4.w * vj);
                 }
-#pragma unroll
-                for (int c = 0; c < NC; ++c) part[c] = warp_sum(part[c]);
-                if (lane == 0) {
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) out[((size_t)(t0 + u) * heads + h) * vdim + col + c] = part[c];
-                }
+                mine[u * 32] = fmaf(vj, cc[u], (a0 + a1) + (a2 + a3));
+            }
+        }
+        __syncthreads();
+        for (int u = w; u < R; u += KW) {
+            if (t0 + u < last && live) {
+                float o = 0.f;
+                for (int q = 0; q < KW; ++q) o += part[((size_t)(p * KW + q) * R + u) * 32 + lane];
+                out[((size_t)(t0 + u) * heads + h) * vdim + col] = o;
             }
         }
     }
+#undef B200H_CDS_LOAD
+    if (!live) return;
 #pragma unroll
-    for (int c = 0; c < NC; ++c)
+    for (int i = 0; i < CK; i += 4) {
+        if (vec && c0 + i < dim) {
+            *reinterpret_cast<float4*>(sp + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        } else {
 #pragma unroll
-        for (int i = 0; i < NW; ++i) { const int d = i * 32 + lane; if (d < dim) sp[(size_t)c * dim + d] = st[c][i]; }
+            for (int e = 0; e < 4; ++e)
+                if (c0 + i + e < dim) sp[i + e] = S[i + e];
+        }
+    }
 }
 
 // y[t] = unit_rms_per_group(o[t]) * w * act(gate[t]) as T: the norm comes before the gate; `groups` equal parts of `count` columns;

@@ -88,9 +88,9 @@ class HybridModel:
         page = slot = 0
         taps = spec.conv_taps
         self.token_off = None
-        if spec.bigram is not None:             # the sequence's last token id, an int in a float's place
+        if spec.bigram is not None:             # the sequence's last token id, an int in a float's place (four floats: what follows stays 16-byte aligned)
             self.token_off = slot
-            slot += 1
+            slot += 4
         for r, (i, _) in enumerate(self.runs):
             layer = spec.layers[i]
             m = layer.mixer
@@ -140,6 +140,7 @@ class HybridModel:
                         raise NotImplementedError("paired mixers: windowed attention beside a channel-decay recurrence in shared-norm blocks")
                     if m.right.dim > 256:
                         raise NotImplementedError("channel-decay recurrence: dim <= 256")
+                    slot = _align(slot, 4)                  # 16-byte reads of the state's columns
                     self.mix_off[r] = slot
                     slot += m.right.heads * m.right.vdim * m.right.dim
                     m = m.left

@@ -121,8 +121,8 @@ def reuse_of_pages_and_slots(make, tol):
 def other_sizes(make, tol):
     """Sizes that a given model may make equal or 1: one layer; one head on each side; as many key/value heads as heads; value
     heads wider and narrower than key heads; every dimension rotated, none rotated; no scaling factor; no chunks, chunks of one
-    position, chunks of a page, chunks longer than the prompt; a recurrence wider than a warp and narrower; an inner decay size
-    of 1; one expert, all experts chosen, one group, as many groups as experts, every group kept; no feed-forward; no second
+    position, chunks of a page, chunks longer than the prompt; a recurrence wider than a warp and narrower, wider than 128 channels,
+    with states that are not 16-byte aligned; an inner decay size of 1; one expert, all experts chosen, one group, as many groups as experts, every group kept; no feed-forward; no second
     embedding table; multipliers larger than the table."""
     L, Lf, R, E, D = FC.layer, FC.left, FC.right, FC.moe, FC.dense
     stacks = [
@@ -134,6 +134,8 @@ def other_sizes(make, tol):
                      L(mlp=D(ff=7)), L(Lf(chunk=0), mlp=E(experts=8, top=2, ff=10, groups=0))], width=40, vocab=33, bigram=(1, 1, 1)),
         dict(layers=[L(mlp=D()), L(Lf(heads=2, kv_heads=1, dim=10, vdim=10, chunk=3, rot_dims=4, factor=8.0), R(heads=2, dim=64, rank=6),
                        mlp=E(experts=6, top=1, ff=16, groups=6, keep=1))], width=24, vocab=20),
+        # a width that leaves the recurrent states unaligned for 16-byte reads; heads wider than 128 channels (a warp per pair of columns)
+        dict(layers=[L(r=R(heads=1, dim=130, rank=3)), L(r=R(heads=2, dim=36, rank=2), mlp=D(ff=9))], width=33, vocab=20),
     ]
     for k, kw in enumerate(stacks):
         cfg = _config(make, **kw)

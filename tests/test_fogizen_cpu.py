@@ -62,10 +62,11 @@ def test_state_and_cache_geometry():
     eng = _make(cfg, FC.random_tensors(cfg))
     model = eng.model
     W = cfg["width"]
-    at, want_shift, want_mix = 1, {}, {}                  # the first float of a slot holds the last token's id
+    at, want_shift, want_mix = 4, {}, {}                  # the first float of a slot holds the last token's id; three pad it
     for r, e in enumerate(cfg["layers"]):
         want_shift[r] = at
         at += 2 * W
+        at = (at + 3) // 4 * 4
         want_mix[r] = at
         at += e["mixer"]["right"]["heads"] * e["mixer"]["right"]["dim"] ** 2
     assert model.token_off == 0 and model.shift_off == want_shift and model.mix_off == want_mix and model.slot_floats == at
