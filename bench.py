@@ -94,10 +94,10 @@ def lifuzen_bench_config(z):
                         "mlp": mlp} for t in HYBRID_LAYERS]}
 
 
-def fogizen_bench_config(z, chunk=1024):
+def fogizen_bench_config(z, chunk=2048):
     """A Fogizen config.json (dict) of size `z`: four shared-norm layers whose paired mixer has the dense decoder's head geometry on
-    its attention side (GQA, 128 dimensions per head of which 64 turn, chunks of 1024 keys) and width / 64 recurrent heads of 64
-    channels (decay matrices of inner size 64) on the other; the first layer's feed-forward is dense with the active size of the
+    its attention side (GQA, 128 dimensions per head of which 64 turn, chunks of 2048 keys: the bench's contexts stay inside the
+    first chunk, so every earlier key is read) and width / 64 recurrent heads of 64 channels (decay matrices of inner size 64) on the other; the first layer's feed-forward is dense with the active size of the
     routed ones (top * ff), the others have eight gated experts in four groups of which two stay eligible and two experts are chosen."""
     d = z["dense"]
     left = {"heads": d["heads"], "kv_heads": d["kv_heads"], "dim": 128, "vdim": 128, "mask": {"size": chunk}, "scale": 128 ** -0.5,

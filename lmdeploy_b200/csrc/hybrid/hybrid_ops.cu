@@ -1213,7 +1213,7 @@ static void launch_window_kernels(const b200h_window_args* a, const WindowGeom& 
         while (tile > 8 && (size_t)H * (H + tile) * sizeof(float) > 96 * 1024) tile /= 2;
         const size_t smem = (size_t)H * (H + tile) * sizeof(float);
         if (smem > 48 * 1024) cudaFuncSetAttribute(window_mix_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        window_mix_scores_kernel<<<a->n, 256, smem, st>>>(g, (const float*)a->talk, tile, (float*)a->ml);
+        window_mix_scores_kernel<<<dim3(a->n, g.rows == 1 ? a->splits : 1), 256, smem, st>>>(g, (const float*)a->talk, tile, (float*)a->ml);
     }
     window_pv_kernel<T, CW, NP><<<dim3(l.blocks, a->splits), 256, l.pv_smem, st>>>(g, (const float*)a->ml, (float*)a->o_part);
 }

@@ -1,13 +1,14 @@
 // Kernels of pre-norm hybrid blocks: table rows added to the stream, residual add fused with an RMS norm, softmax attention
-// with grouped key/value heads over a sliding window of a paged cache (capped scores, a logarithmic distance penalty, the
-// heads' weight rows recombined by a matrix after the softmax, an output gate), and the squared-relu activation.
+// with grouped key/value heads over a sliding window or within chunks of a paged cache (capped scores, a logarithmic distance
+// penalty, the heads' weight rows recombined by a matrix after the softmax or their scores before it, a sink, an output gate per
+// column or per head), the preparation of an attention that norms per head and rotates, and the squared-relu activation.
 // Included by hybrid_ops.cu inside namespace b200h, after its helpers (to_f / from_f / block_sum / sigmoid_f).
 //
 // Cache entry of position p of a sequence, inside its page (page address + layer_off): the normed key as T at
 // [p % block_len][kv_heads * dim], and, v_off bytes further, the value as T at [p % block_len][kv_heads * vdim].
 //
-// Attention runs in two passes over a row's visible keys [max(0, pos - window + 1), pos], both cut into `splits` equal key
-// ranges so that a step of few rows still fills the SMs:
+// Attention runs in two passes over a row's visible keys [window_first(pos), pos] -- the window's first key, or the first key of
+// the row's chunk --, both cut into `splits` equal key ranges so that a step of few rows still fills the SMs:
 //   pass 1 (window_stats_kernel, one block per row block, key/value head and range): scores of the heads that share the key/value
 //          head, written to a scratch [row, head, key - first visible key], and their running maximum and denominator;
 //   pass 2 (window_pv_kernel, one block per row block and range): the ranges' (maximum, denominator) pairs are merged per head, the
@@ -15,6 +16,8 @@
 //          (weight'_h = sum_g talk[h, g] weight_g -- this couples every head of a row, hence one block for all of them) and
 //          applied to the values of each head's own key/value head;
 //   window_out_kernel sums the ranges' partial outputs, applies sigmoid(gate) and writes T.
+// A design that mixes the heads' SCORES runs window_mix_scores_kernel between the passes (scores mixed in place, maxima and
+// denominators recomputed from the mixed scores) and pass 2 without its recombination.
 // A block takes `rows` consecutive rows of the step; those of one sequence (consecutive positions) walk their keys together, so a
 // cached key or value is read and converted once for all of them (prompt portions: 4 rows; a step of single tokens: 1).
 // Scores, softmax, recombination and the weighted value sums are float whatever T is.
@@ -465,43 +468,48 @@ __global__ void window_out_kernel(const float* __restrict__ o_part, int splits, 
 }
 
 // Scores mixed ACROSS heads before the softmax: for every row and visible key, s'_h = sum_g talk[h, g] s_g, in place in the
-// scratch pass 1 left, then every (row, head)'s running maximum and denominator over the mixed scores (into key range 0; the
-// other ranges get the neutral pair, pass 2 merges them all).  One block per row; a tile of keys of all heads passes through
-// shared memory: talk [heads][heads] | tile [heads][keys] floats.
+// scratch pass 1 left, then every (row, head)'s running maximum and denominator over the mixed scores of the block's key range
+// (pass 2 merges the ranges).  grid (rows, splits): a block takes key range blockIdx.y of ONE row -- the ranges pass 1 used when it
+// cut a row's keys (one row per block there), the whole row otherwise; a tile of keys of all heads passes through shared memory:
+// talk [heads][heads] | tile [heads][keys] floats.
 __global__ void __launch_bounds__(256) window_mix_scores_kernel(WindowGeom g, const float* __restrict__ talk, int tile, float* __restrict__ ml)
 {
     extern __shared__ __align__(16) float mix_smem[];
-    const int t = blockIdx.x, H = g.heads, tid = threadIdx.x, nt = blockDim.x;
-    const int pos = g.tok_pos[t], keys = pos - window_first(g, pos) + 1;
+    const int t = blockIdx.x, z = blockIdx.y, H = g.heads, tid = threadIdx.x, nt = blockDim.x;
+    const int pos = g.tok_pos[t], lo = window_first(g, pos);
+    int j0, j1;
+    window_range(g, pos, pos, z, j0, j1);
+    j0 -= lo;                                                 // the scratch is indexed from the row's first visible key
+    j1 -= lo;
     float* tk = mix_smem;
     float* raw = mix_smem + H * H;
     float* row = g.scores + (size_t)t * H * g.score_ld;
     for (int i = tid; i < H * H; i += nt) tk[i] = talk[i];
-    for (int j0 = 0; j0 < keys; j0 += tile) {
-        const int kt = min(tile, keys - j0);
+    for (int jt = j0; jt < j1; jt += tile) {
+        const int kt = min(tile, j1 - jt);
         __syncthreads();
-        for (int i = tid; i < H * kt; i += nt) { const int h = i / kt, jj = i - h * kt; raw[h * tile + jj] = row[(size_t)h * g.score_ld + j0 + jj]; }
+        for (int i = tid; i < H * kt; i += nt) { const int h = i / kt, jj = i - h * kt; raw[h * tile + jj] = row[(size_t)h * g.score_ld + jt + jj]; }
         __syncthreads();
         for (int i = tid; i < H * kt; i += nt) {
             const int h = i / kt, jj = i - h * kt;
             float a = 0.f;
             for (int k = 0; k < H; ++k) a = fmaf(tk[h * H + k], raw[k * tile + jj], a);
-            row[(size_t)h * g.score_ld + j0 + jj] = a;
+            row[(size_t)h * g.score_ld + jt + jj] = a;
         }
     }
     __syncthreads();
     const int lane = tid & 31, warp = tid >> 5, nw = nt >> 5;
     for (int h = warp; h < H; h += nw) {
         float m = -1e30f, l = 0.f;
-        for (int j = lane; j < keys; j += 32) merge_ml(m, l, row[(size_t)h * g.score_ld + j], 1.0f);
+        for (int j = j0 + lane; j < j1; j += 32) merge_ml(m, l, row[(size_t)h * g.score_ld + j], 1.0f);
         for (int o = 16; o > 0; o >>= 1) {
             const float om = __shfl_xor_sync(0xffffffffu, m, o), ol = __shfl_xor_sync(0xffffffffu, l, o);
             merge_ml(m, l, om, ol);
         }
-        float* dst = ml + ((size_t)t * H + h) * g.splits * 2;
-        for (int z = lane; z < g.splits; z += 32) {
-            dst[2 * z] = z == 0 ? m : -1e30f;
-            dst[2 * z + 1] = z == 0 ? l : 0.f;
+        if (lane == 0) {
+            float* dst = ml + (((size_t)t * H + h) * g.splits + z) * 2;
+            dst[0] = m;
+            dst[1] = l;
         }
     }
 }
