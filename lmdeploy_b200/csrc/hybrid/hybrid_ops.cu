@@ -1484,6 +1484,15 @@ B200H_API int b200h_group_norm_gate(const void* o, const void* w, const void* ga
         return fail(B200H_ERR_INVALID_ARG, "group_norm_gate: bad arguments");
     if (n == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
+    const int gw = count / groups;
+#define B200H_GNG(NV)                                                                                                                      \
+    group_norm_gate_warp_kernel<T, NV><<<n, groups >= 8 ? 256 : 32 * groups, 0, st>>>((const float*)o, (const float*)w, (const T*)gate, ld_gate, \
+                                                                                     count, groups, act, eps, (T*)y)
+    if (gw <= 256) {            // a warp per group
+        B200H_DISPATCH_T(dtype, if (gw <= 32) B200H_GNG(1); else if (gw <= 64) B200H_GNG(2); else if (gw <= 128) B200H_GNG(4); else B200H_GNG(8));
+        return launched("group_norm_gate");
+    }
+#undef B200H_GNG
     B200H_DISPATCH_T(dtype, group_norm_gate_kernel<T><<<dim3(n, groups), 128, 0, st>>>((const float*)o, (const float*)w, (const T*)gate, ld_gate,
                                                                                       count, groups, act, eps, (T*)y));
     return launched("group_norm_gate");

@@ -281,6 +281,34 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ o, const float*
     }
 }
 
+// The same for groups of at most a few hundred columns (a head): one block per row, a WARP per group at a time -- the group's
+// values stay in the lanes' registers between the sum of squares and the scaling, and nothing waits at a block barrier.
+// NV = ceil(group width / 32) values per lane.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256) group_norm_gate_warp_kernel(const float* __restrict__ o, const float* __restrict__ w,
+                                                                  const T* __restrict__ gate, int64_t ld_gate, int count, int groups, int act,
+                                                                  float eps, T* __restrict__ y)
+{
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, gw = count / groups;
+    for (int g = warp; g < groups; g += nw) {
+        const size_t at = (size_t)g * gw;
+        const float* ot = o + (size_t)t * count + at;
+        float v[NV], ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) { const int c = i * 32 + lane; v[i] = c < gw ? ot[c] : 0.f; ss += v[i] * v[i]; }
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float)gw + eps);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = i * 32 + lane;
+            if (c < gw) {
+                const float z = to_f(gate[(size_t)t * ld_gate + at + c]);
+                y[(size_t)t * count + at + c] = from_f<T>(v[i] * r * w[at + c] * (act ? silu_f(z) : sigmoid_f(z)));
+            }
+        }
+    }
+}
+
 // x <- z > 0 ? softplus(p) z^2 + z / 2 : (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2, in place (T); params = {p, q} (float, device)
 template <typename T>
 __global__ void xielu_kernel(T* __restrict__ x, int64_t count, const float* __restrict__ params)
