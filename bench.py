@@ -101,13 +101,13 @@ def fogizen_bench_config(z, chunk=2048):
     routed ones (top * ff), the others have eight gated experts in four groups of which two stay eligible and two experts are chosen."""
     d = z["dense"]
     left = {"heads": d["heads"], "kv_heads": d["kv_heads"], "dim": 128, "vdim": 128, "mask": {"size": chunk}, "scale": 128 ** -0.5,
-            "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 2.0}}}
+            "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0}}}
     right = {"heads": z["width"] // 64, "dim": 64, "rank": 64}
     moe = {"kind": "moe", "expert": {"ff": z["ff"]},
-           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.0, "groups": {"count": z["experts"] // 2, "keep": z["experts"] // 4}}}
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": z["experts"] // 2, "keep": z["experts"] // 4}}}
     dense = {"kind": "dense", "ff": z["top"] * z["ff"]}
     return {"architecture": "Fogizen", "norm": {"eps": 1e-6}, "vocab": HYBRID_VOCAB, "width": z["width"],
-            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 127}},
             "layers": [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": dense if i == 0 else moe}
                        for i in range(len(HYBRID_LAYERS))]}
 

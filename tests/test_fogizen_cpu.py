@@ -143,3 +143,17 @@ def test_oracle_activation_and_router():
     p["correction"] = torch.tensor([0.0, 0.0, -0.2, 0.0], dtype=torch.float64)
     (e, wt), = F.route(torch.tensor([1.0], dtype=torch.float64), p, f)          # 0.9 + 0.1 = 1.0 against 0.4 + 0.5: group 0 wins on a tie? no: 1.0 > 0.9
     assert e == 0
+
+
+def test_bench_configuration_builds_a_spec():
+    """The sizes bench.py --hybrid-design fogizen runs parse into a spec whose tensors have the expected shapes."""
+    import bench
+    from lmdeploy_b200.turbomind.hybrid import HybridModel
+    from lmdeploy_b200.turbomind.specs import fogizen_spec
+    for size, z in bench.HYBRID_SIZES.items():
+        spec = fogizen_spec(bench.fogizen_bench_config(z), name=size)
+        assert len(spec.layers) == 4 and spec.layers[0].mlp.kind == "dense" and all(l.mlp.kind == "moe" for l in spec.layers[1:])
+        shapes = HybridModel.tensor_shapes(FC._Shapes(spec))
+        W = z["width"]
+        assert shapes["l0.mix.right.w1"] == (64, W) and shapes["l3.mix.left.g"] == (z["dense"]["heads"], W)
+        assert shapes["bigram"] == (65522, W) and shapes["l1.mlp.correction"] == (z["experts"],)
